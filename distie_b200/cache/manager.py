@@ -29,7 +29,9 @@ values live in one device slab per group, indexed by those ids.
   and the window.
 * A group whose need names a ``chunk`` gives pages back like a windowed one: no later
   position reads a key from before the chunk the request is in.  A group whose values
-  have another size than its keys keeps two slabs instead of one.
+  have another size than its keys keeps two slabs instead of one; a group whose values lie
+  inside its keys (``values_in_keys``: the latent rows of an attention through a latent) keeps
+  keys only, and ``KvSlot.v`` is a view of their first columns.
 
 With ``device=None`` the manager keeps only the bookkeeping (no slabs), which is
 what the scheduler tests and sizing estimates use.
@@ -60,7 +62,7 @@ def pages_needed(tokens: int, page_size: int) -> int:
 def pages_that_fit(cache_needs, page_size: int, element_size: int, budget_bytes: int) -> int:
     """How many pages per group ``budget_bytes`` of device memory hold (the spare page of every slab included
     in the budget, not in the count): every cache slot keeps keys and values of its own for each page id."""
-    per_page = sum(need.num_kv_heads * (need.head_dim + need.v_dim) * element_size * page_size for need in cache_needs.values())
+    per_page = sum(need.num_kv_heads * need.row_elements * element_size * page_size for need in cache_needs.values())
     if per_page <= 0:
         raise ValueError("the model declares no cache to size")
     return int(budget_bytes // per_page) - 1
@@ -99,7 +101,7 @@ class KvGroup:
         self._uploaded = None  # CUDA event after the last upload: the pinned table waits for it before it changes
 
     def bytes_per_token(self, element_size: int) -> int:
-        return len(self.slots) * self.need.num_kv_heads * (self.need.head_dim + self.need.v_dim) * element_size
+        return len(self.slots) * self.need.num_kv_heads * self.need.row_elements * element_size
 
     # -- bookkeeping --------------------------------------------------------
     def first_needed_page(self, cached: int) -> int:
@@ -179,7 +181,10 @@ class KvGroup:
     # -- device side --------------------------------------------------------
     def allocate_device(self, dtype: torch.dtype, device: torch.device) -> None:
         rows = (self.num_pages + 1, self.need.num_kv_heads, self.page_size)
-        if self.need.v_dim == self.need.head_dim:
+        if self.need.values_in_keys:  # one row per token; a value is the head of its key's row
+            self._keys = torch.zeros((len(self.slots), *rows, self.need.head_dim), dtype=dtype, device=device)
+            self._values = self._keys[..., : self.need.v_dim]
+        elif self.need.v_dim == self.need.head_dim:
             self.slab = torch.zeros((len(self.slots), 2, *rows, self.need.head_dim), dtype=dtype, device=device)
             self._keys, self._values = self.slab[:, 0], self.slab[:, 1]
         else:  # values of another size than keys: a slab each

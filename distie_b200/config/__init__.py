@@ -5,6 +5,7 @@ from .model_spec import LayerCall, LayerSpec, ModelSpec, PartSpec
 from .qwen2_config import ConfigError, Qwen2Config
 from .fovudra_config import FovudraConfig
 from .zelasun_config import ZelasunConfig
+from .zururax_config import ZururaxConfig
 from .registry import (
     Architecture,
     architecture_of,
@@ -26,6 +27,7 @@ __all__ = [
     "PartSpec",
     "Qwen2Config",
     "ZelasunConfig",
+    "ZururaxConfig",
     "architecture_of",
     "get_architecture",
     "known_architectures",

@@ -49,6 +49,8 @@ CUDA_UNITS: dict[str, list[str]] = {
     "state": ["recurrent.cu"],
     # models whose feed-forward routes tokens to experts (both dtypes)
     "routed": ["routed.cu"],
+    # models whose attention reads one latent row per token; gated and squared-ReLU activations on float32 products
+    "latent": ["latent.cu"],
 }
 _HEADERS = ["common.cuh", "tcgen05.cuh", "no_alloc.h"]
 

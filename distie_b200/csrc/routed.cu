@@ -21,9 +21,81 @@ namespace distie {
 
 __device__ __forceinline__ float routed_silu(float z) { return z / (1.f + expf(-z)); }
 __device__ __forceinline__ float routed_sigmoid(float z) { return 1.f / (1.f + expf(-z)); }
+// The hidden activation of an expert: silu(g) * u, or with limit > 0 the capped form
+// g' = min(g, limit), u' = clamp(u, -limit, limit), g' * sigmoid(1.702 g') * (u' + 1).
+__device__ __forceinline__ float routed_glu(float g, float u, float limit) {
+  if (limit > 0.f) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g * routed_sigmoid(1.702f * g) * (u + 1.f);
+  }
+  return routed_silu(g) * u;
+}
 
 constexpr int kRouteThreads = 256;
 constexpr int kMaxTop = 32;
+
+// A warp picks for one token.  `mine` holds the token's `experts` scores in shared memory and `group_s` has room for
+// `count` floats.  With count > 1 and keep < count the experts form `count` equal groups of neighbours; a group's
+// score is the sum of its two largest scores (of its one score in groups of one) and only the experts of the `keep`
+// best groups (ties to the lower group) stay eligible.  Then the `top` largest eligible scores, ties to the lower
+// index; the weights are the scores times `weight_scale`.
+__device__ __forceinline__ void route_choose(float* mine, float* group_s, int experts, int top, int count, int keep,
+                                             float weight_scale, int* __restrict__ ids, float* __restrict__ weights,
+                                             int lane) {
+  if (count > 1 && keep < count) {
+    const int size = experts / count;
+    for (int g = lane; g < count; g += 32) {
+      float first = -1.f, second = -1.f;
+      for (int i = 0; i < size; ++i) {
+        const float sc = mine[g * size + i];
+        if (sc > first) { second = first; first = sc; }
+        else if (sc > second) second = sc;
+      }
+      group_s[g] = size > 1 ? first + second : first;
+    }
+    __syncwarp();
+    for (int j = 0; j < keep; ++j) {
+      float best = -1.f;  // group scores lie in [0, 2]; a group kept is set to -3
+      int at = count;
+      for (int g = lane; g < count; g += 32) {
+        const float sc = group_s[g];
+        if (sc > best) { best = sc; at = g; }
+      }
+#pragma unroll
+      for (int offset = 16; offset > 0; offset >>= 1) {
+        const float other = __shfl_xor_sync(0xffffffffu, best, offset);
+        const int other_at = __shfl_xor_sync(0xffffffffu, at, offset);
+        if (other > best || (other == best && other_at < at)) { best = other; at = other_at; }
+      }
+      if (lane == 0 && at < count) group_s[at] = -3.f;
+      __syncwarp();
+    }
+    for (int e = lane; e < experts; e += 32)
+      if (group_s[e / size] != -3.f) mine[e] = -2.f;
+    __syncwarp();
+  }
+  for (int j = 0; j < top; ++j) {
+    float best = -1.f;  // scores lie in [0, 1]; a score taken or not eligible is -2
+    int at = experts;
+    for (int e = lane; e < experts; e += 32) {
+      const float sc = mine[e];
+      if (sc > best) { best = sc; at = e; }  // the first of equal scores within a lane: the lower index
+    }
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+      const float other = __shfl_xor_sync(0xffffffffu, best, offset);
+      const int other_at = __shfl_xor_sync(0xffffffffu, at, offset);
+      if (other > best || (other == best && other_at < at)) { best = other; at = other_at; }
+    }
+    if (lane == 0) {
+      ids[j] = at;
+      weights[j] = best * weight_scale;
+      mine[at] = -2.f;
+    }
+    __syncwarp();
+  }
+}
 
 // TOK tokens a block: their rows wait in shared memory as floats and a warp takes an expert at a time for all of
 // them, so a router row is read once per TOK tokens, in runs of VEC elements a lane.  Then a warp per token picks
@@ -31,10 +103,12 @@ constexpr int kMaxTop = 32;
 template <typename T, int TOK, int VEC>
 __global__ void __launch_bounds__(kRouteThreads)
 route_top_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ router, int tokens, int hidden, int experts,
-                 int top, int* __restrict__ ids, float* __restrict__ weights) {
+                 int top, int* __restrict__ ids, float* __restrict__ weights, int group_count, int group_keep,
+                 float weight_scale, int extra, float* __restrict__ extra_out) {
   extern __shared__ __align__(16) float route_s[];
   float* x_s = route_s;
-  float* scores_s = route_s + (size_t)TOK * hidden;
+  float* scores_s = route_s + (size_t)TOK * hidden;  // per token: experts scores, then group_count floats
+  const int score_row = experts + group_count;
   const int t0 = blockIdx.x * TOK, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int live = min(TOK, tokens - t0);
   for (int r = 0; r < TOK; ++r) {
@@ -54,7 +128,7 @@ route_top_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ ro
     }
   }
   __syncthreads();
-  for (int e = warp; e < experts; e += kRouteThreads / 32) {
+  for (int e = warp; e < experts + extra; e += kRouteThreads / 32) {  // rows past the experts': logits handed out as they are
     const T* w = router + (size_t)e * hidden;
     float dot[TOK];
 #pragma unroll
@@ -80,67 +154,33 @@ route_top_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ ro
 #pragma unroll
     for (int r = 0; r < TOK; ++r) {
       const float z = warp_sum(dot[r]);
-      if (lane == 0) scores_s[r * experts + e] = routed_sigmoid(z);
+      if (lane == 0) {
+        if (e < experts) scores_s[r * score_row + e] = routed_sigmoid(z);
+        else if (r < live) extra_out[(size_t)(t0 + r) * extra + e - experts] = z;
+      }
     }
   }
   __syncthreads();
   for (int r = warp; r < live; r += kRouteThreads / 32) {
-    float* mine = scores_s + (size_t)r * experts;
+    float* mine = scores_s + (size_t)r * score_row;
     const size_t t = t0 + r;
-    for (int j = 0; j < top; ++j) {
-      float best = -1.f;  // scores lie in [0, 1]; a score taken is set to -2
-      int at = experts;
-      for (int e = lane; e < experts; e += 32) {
-        const float sc = mine[e];
-        if (sc > best) { best = sc; at = e; }  // the first of equal scores within a lane: the lower index
-      }
-#pragma unroll
-      for (int offset = 16; offset > 0; offset >>= 1) {
-        const float other = __shfl_xor_sync(0xffffffffu, best, offset);
-        const int other_at = __shfl_xor_sync(0xffffffffu, at, offset);
-        if (other > best || (other == best && other_at < at)) { best = other; at = other_at; }
-      }
-      if (lane == 0) {
-        ids[t * top + j] = at;
-        weights[t * top + j] = best;
-        mine[at] = -2.f;
-      }
-      __syncwarp();
-    }
+    route_choose(mine, mine + experts, experts, top, group_count, group_keep, weight_scale, ids + t * top, weights + t * top, lane);
   }
 }
 
 // The choice alone, from float32 logits [tokens, experts] that a product left: a warp per token.
 __global__ void __launch_bounds__(kRouteThreads)
 route_pick_kernel(const float* __restrict__ logits, int logit_stride, int tokens, int experts, int top,
-                  int* __restrict__ ids, float* __restrict__ weights) {
-  extern __shared__ float pick_s[];  // a row of scores per warp
+                  int* __restrict__ ids, float* __restrict__ weights, int group_count, int group_keep, float weight_scale) {
+  extern __shared__ float pick_s[];  // per warp: a row of scores, then group_count floats
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int t = blockIdx.x * (kRouteThreads / 32) + warp;
   if (t >= tokens) return;
-  float* mine = pick_s + (size_t)warp * experts;
+  float* mine = pick_s + (size_t)warp * (experts + group_count);
   for (int e = lane; e < experts; e += 32) mine[e] = routed_sigmoid(logits[(size_t)t * logit_stride + e]);
   __syncwarp();
-  for (int j = 0; j < top; ++j) {
-    float best = -1.f;
-    int at = experts;
-    for (int e = lane; e < experts; e += 32) {
-      const float sc = mine[e];
-      if (sc > best) { best = sc; at = e; }
-    }
-#pragma unroll
-    for (int offset = 16; offset > 0; offset >>= 1) {
-      const float other = __shfl_xor_sync(0xffffffffu, best, offset);
-      const int other_at = __shfl_xor_sync(0xffffffffu, at, offset);
-      if (other > best || (other == best && other_at < at)) { best = other; at = other_at; }
-    }
-    if (lane == 0) {
-      ids[(size_t)t * top + j] = at;
-      weights[(size_t)t * top + j] = best;
-      mine[at] = -2.f;
-    }
-    __syncwarp();
-  }
+  route_choose(mine, mine + experts, experts, top, group_count, group_keep, weight_scale, ids + (size_t)t * top,
+               weights + (size_t)t * top, lane);
 }
 
 // plan layout (int32): [0] number of tiles; [1 .. 1 + experts] offsets of the experts' slots; then
@@ -228,7 +268,7 @@ template <typename T, bool SWIGLU>
 __global__ void __launch_bounds__(kGroupedThreads)
 grouped_product_kernel(const T* __restrict__ a, int a_stride, const T* __restrict__ w, int* __restrict__ plan_base,
                        int pairs, int experts, T* __restrict__ out, float* __restrict__ out32, int N, int K, int gather,
-                       int scale_in, int scale_out) {
+                       int scale_in, int scale_out, float limit) {
   const RoutePlan plan = plan_views(plan_base, pairs, experts, kTileM);
   const int tile = blockIdx.x;
   if (tile >= *plan.num_tiles) return;
@@ -293,7 +333,7 @@ grouped_product_kernel(const T* __restrict__ a, int a_stride, const T* __restric
       const int n = n0 + 4 * tx + c;
       if (n >= N) continue;
       if (SWIGLU) {
-        out[(size_t)slot * N + n] = from_float<T>(routed_silu(acc[r][c]) * acc_up[r][c]);
+        out[(size_t)slot * N + n] = from_float<T>(routed_glu(acc[r][c], acc_up[r][c], limit));
       } else {
         const float v = scale_out ? acc[r][c] * scale_s[local] : acc[r][c];
         out32[(size_t)plan.dest[slot] * N + n] = v;
@@ -312,7 +352,7 @@ template <bool SWIGLU>
 __global__ void __launch_bounds__(kMmaThreads)
 grouped_product_mma_kernel(const __nv_bfloat16* __restrict__ a, int a_stride, const __nv_bfloat16* __restrict__ w,
                            int* __restrict__ plan_base, int pairs, int experts, __nv_bfloat16* __restrict__ out,
-                           float* __restrict__ out32, int N, int K, int gather, int scale_in, int scale_out) {
+                           float* __restrict__ out32, int N, int K, int gather, int scale_in, int scale_out, float limit) {
   using namespace nvcuda;
   const RoutePlan plan = plan_views(plan_base, pairs, experts, kMmaM);
   const int tile = blockIdx.x;
@@ -387,7 +427,7 @@ grouped_product_mma_kernel(const __nv_bfloat16* __restrict__ a, int a_stride, co
   for (int i = 0; i < 2; ++i) {
     if (SWIGLU) {
 #pragma unroll
-      for (int e = 0; e < acc[i].num_elements; ++e) acc[i].x[e] = routed_silu(acc[i].x[e]) * acc_up[i].x[e];
+      for (int e = 0; e < acc[i].num_elements; ++e) acc[i].x[e] = routed_glu(acc[i].x[e], acc_up[i].x[e], limit);
     }
     wmma::store_matrix_sync(&c_s[warp][0][0], acc[i], 16 + 4, wmma::mem_row_major);
     __syncwarp();
@@ -467,7 +507,7 @@ template <typename T, bool SWIGLU, int VEC>
 __global__ void __launch_bounds__(kRowsWarps * 32, 3)
 grouped_rows_kernel(int rounds, const T* __restrict__ a, int a_stride, const T* __restrict__ w, int* __restrict__ plan_base, int pairs,
                     int experts, T* __restrict__ out, float* __restrict__ out32, int N, int K, int gather, int scale_in,
-                    int scale_out) {
+                    int scale_out, float limit) {
   extern __shared__ __align__(16) unsigned char rows_raw[];
   T* a_s = reinterpret_cast<T*>(rows_raw);  // [kRowsR][K]
   __shared__ int src_s[kRowsR];
@@ -551,7 +591,7 @@ grouped_rows_kernel(int rounds, const T* __restrict__ a, int a_stride, const T* 
         if (r == lane) { v0 = acc0[r]; v1 = acc1[r]; }
       const int slot = first + lane;
       if (SWIGLU) {
-        out[(size_t)slot * N + n] = from_float<T>(routed_silu(v0) * v1);
+        out[(size_t)slot * N + n] = from_float<T>(routed_glu(v0, v1, limit));
       } else {
         const float s = scale_out ? scale_s[lane] : 1.f;
         float* dst = out32 + (size_t)plan.dest[slot] * N + n;
@@ -564,7 +604,7 @@ grouped_rows_kernel(int rounds, const T* __restrict__ a, int a_stride, const T* 
 
 template <typename T, bool SWIGLU>
 static int launch_grouped_rows(const T* a, int a_stride, const T* w, int* plan, int pairs, int experts, T* out, float* out32,
-                               int N, int K, int gather, int scale_in, int scale_out, unsigned max_tiles, cudaStream_t stream) {
+                               int N, int K, int gather, int scale_in, int scale_out, float limit, unsigned max_tiles, cudaStream_t stream) {
   constexpr int WIDE = sizeof(T) == 2 ? 8 : 4;
   const bool vec = K % WIDE == 0 && a_stride % WIDE == 0 && (((uintptr_t)a | (uintptr_t)w) & 15) == 0;
   const size_t shared = (size_t)kRowsR * K * sizeof(T);
@@ -575,7 +615,7 @@ static int launch_grouped_rows(const T* a, int a_stride, const T* w, int* plan, 
   auto run = [&](auto kernel) {
     if (shared > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
     kernel<<<grid, kRowsWarps * 32, shared, stream>>>(rounds, a, a_stride, w, plan, pairs, experts, out, out32, N, K, gather, scale_in,
-                                                     scale_out);
+                                                     scale_out, limit);
   };
   if (vec) run(grouped_rows_kernel<T, SWIGLU, WIDE>);
   else run(grouped_rows_kernel<T, SWIGLU, 1>);
@@ -589,19 +629,24 @@ using namespace distie;
 
 // x [tokens, hidden] and router [experts, hidden] of one type; ids, weights [tokens, top].
 extern "C" int distie_route_top(const void* x, int x_stride, const void* router, int tokens, int hidden, int experts,
-                                int top, int* ids, float* weights, int dtype, cudaStream_t stream) {
+                                int top, int* ids, float* weights, int group_count, int group_keep, float weight_scale,
+                                int extra, float* extra_out, int dtype, cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (hidden < 1 || experts < 1 || top < 1 || top > experts || top > kMaxTop || experts > 8192) return DISTIE_ERR_ARG;
+  if (hidden < 1 || experts < 1 || top < 1 || top > experts || top > kMaxTop || experts > 8192 || group_count < 1 ||
+      experts % group_count != 0 || group_keep < 1 || group_keep > group_count || extra < 0 || (extra > 0 && !extra_out) ||
+      top > group_keep * (experts / group_count))
+    return DISTIE_ERR_ARG;
   if (dtype != DISTIE_BF16 && dtype != DISTIE_F32) return DISTIE_ERR_UNSUPPORTED;
   const int wide = dtype == DISTIE_BF16 ? 8 : 4;
   const bool vec = hidden % wide == 0 && ((uintptr_t)router & 15) == 0;
-  const int tok = tokens >= 64 && (size_t)4 * (hidden + experts) * sizeof(float) <= 96 * 1024 ? 4 : 1;
-  const size_t shared = (size_t)tok * (hidden + experts) * sizeof(float);
+  const int tok = tokens >= 64 && (size_t)4 * (hidden + experts + group_count) * sizeof(float) <= 96 * 1024 ? 4 : 1;
+  const size_t shared = (size_t)tok * (hidden + experts + group_count) * sizeof(float);
   if (shared > 200 * 1024) return DISTIE_ERR_UNSUPPORTED;
   const unsigned blocks = (unsigned)((tokens + tok - 1) / tok);
   auto run = [&](auto kernel, auto xp, auto rp) {
     if (shared > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
-    kernel<<<blocks, kRouteThreads, shared, stream>>>(xp, x_stride, rp, tokens, hidden, experts, top, ids, weights);
+    kernel<<<blocks, kRouteThreads, shared, stream>>>(xp, x_stride, rp, tokens, hidden, experts, top, ids, weights, group_count,
+                                                      group_keep, weight_scale, extra, extra_out);
   };
 #define DISTIE_ROUTE(T, VECV)                                                                             \
   do {                                                                                                    \
@@ -634,7 +679,7 @@ extern "C" long long distie_route_plan_words(int pairs, int experts, int tile) {
 // weight_on_input: the pair's weight multiplies the expert's input, else its output.
 extern "C" int distie_routed_swiglu(const void* x, int x_stride, const int* ids, const float* weights, const void* gate_up,
                                     const void* down, int* plan, void* mid, float* out, int tokens, int top, int experts,
-                                    int hidden, int ff, int weight_on_input, int dtype, int* error, cudaStream_t stream) {
+                                    int hidden, int ff, int weight_on_input, float limit, int dtype, int* error, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (top < 1 || experts < 1 || hidden < 1 || ff < 1 || experts > 4096) return DISTIE_ERR_ARG;
   if (dtype != DISTIE_BF16 && dtype != DISTIE_F32) return DISTIE_ERR_UNSUPPORTED;
@@ -653,26 +698,26 @@ extern "C" int distie_routed_swiglu(const void* x, int x_stride, const int* ids,
     if (dtype == DISTIE_BF16) {
       status = launch_grouped_rows<__nv_bfloat16, true>((const __nv_bfloat16*)x, x_stride, (const __nv_bfloat16*)gate_up, plan,
                                                         pairs, experts, (__nv_bfloat16*)mid, nullptr, ff, hidden, 1, in, 0,
-                                                        max_tiles, stream);
+                                                        limit, max_tiles, stream);
       if (status != 0) return status;
       return launch_grouped_rows<__nv_bfloat16, false>((const __nv_bfloat16*)mid, ff, (const __nv_bfloat16*)down, plan, pairs,
-                                                       experts, nullptr, out, hidden, ff, 0, 0, 1 - in, max_tiles, stream);
+                                                       experts, nullptr, out, hidden, ff, 0, 0, 1 - in, 0.f, max_tiles, stream);
     }
     status = launch_grouped_rows<float, true>((const float*)x, x_stride, (const float*)gate_up, plan, pairs, experts,
-                                              (float*)mid, nullptr, ff, hidden, 1, in, 0, max_tiles, stream);
+                                              (float*)mid, nullptr, ff, hidden, 1, in, 0, limit, max_tiles, stream);
     if (status != 0) return status;
     return launch_grouped_rows<float, false>((const float*)mid, ff, (const float*)down, plan, pairs, experts, nullptr, out,
-                                             hidden, ff, 0, 0, 1 - in, max_tiles, stream);
+                                             hidden, ff, 0, 0, 1 - in, 0.f, max_tiles, stream);
   }
   if (mma) {
     const dim3 up_grid(max_tiles, (ff + kMmaN - 1) / kMmaN), down_grid(max_tiles, (hidden + kMmaN - 1) / kMmaN);
     grouped_product_mma_kernel<true><<<up_grid, kMmaThreads, 0, stream>>>(
         (const __nv_bfloat16*)x, x_stride, (const __nv_bfloat16*)gate_up, plan, pairs, experts, (__nv_bfloat16*)mid,
-        nullptr, ff, hidden, 1, in, 0);
+        nullptr, ff, hidden, 1, in, 0, limit);
     DISTIE_LAUNCH_CHECK();
     grouped_product_mma_kernel<false><<<down_grid, kMmaThreads, 0, stream>>>(
         (const __nv_bfloat16*)mid, ff, (const __nv_bfloat16*)down, plan, pairs, experts, nullptr, out, hidden, ff, 0, 0,
-        1 - in);
+        1 - in, 0.f);
     DISTIE_LAUNCH_CHECK();
     return 0;
   }
@@ -680,17 +725,17 @@ extern "C" int distie_routed_swiglu(const void* x, int x_stride, const int* ids,
   if (dtype == DISTIE_BF16) {
     grouped_product_kernel<__nv_bfloat16, true><<<up_grid, kGroupedThreads, 0, stream>>>(
         (const __nv_bfloat16*)x, x_stride, (const __nv_bfloat16*)gate_up, plan, pairs, experts, (__nv_bfloat16*)mid,
-        nullptr, ff, hidden, 1, in, 0);
+        nullptr, ff, hidden, 1, in, 0, limit);
     DISTIE_LAUNCH_CHECK();
     grouped_product_kernel<__nv_bfloat16, false><<<down_grid, kGroupedThreads, 0, stream>>>(
         (const __nv_bfloat16*)mid, ff, (const __nv_bfloat16*)down, plan, pairs, experts, nullptr, out, hidden, ff, 0, 0,
-        1 - in);
+        1 - in, 0.f);
   } else {
     grouped_product_kernel<float, true><<<up_grid, kGroupedThreads, 0, stream>>>(
-        (const float*)x, x_stride, (const float*)gate_up, plan, pairs, experts, (float*)mid, nullptr, ff, hidden, 1, in, 0);
+        (const float*)x, x_stride, (const float*)gate_up, plan, pairs, experts, (float*)mid, nullptr, ff, hidden, 1, in, 0, limit);
     DISTIE_LAUNCH_CHECK();
     grouped_product_kernel<float, false><<<down_grid, kGroupedThreads, 0, stream>>>(
-        (const float*)mid, ff, (const float*)down, plan, pairs, experts, nullptr, out, hidden, ff, 0, 0, 1 - in);
+        (const float*)mid, ff, (const float*)down, plan, pairs, experts, nullptr, out, hidden, ff, 0, 0, 1 - in, 0.f);
   }
   DISTIE_LAUNCH_CHECK();
   return 0;
@@ -732,14 +777,17 @@ extern "C" int distie_routed_scatter(const float* y, int* plan, int pairs, int e
 
 // ids and weights from float32 logits [tokens, experts] (row stride logit_stride): see route_pick_kernel.
 extern "C" int distie_route_pick(const float* logits, int logit_stride, int tokens, int experts, int top, int* ids,
-                                 float* weights, cudaStream_t stream) {
+                                 float* weights, int group_count, int group_keep, float weight_scale, cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (experts < 1 || top < 1 || top > experts || top > kMaxTop || experts > 4096) return DISTIE_ERR_ARG;
+  if (experts < 1 || top < 1 || top > experts || top > kMaxTop || experts > 4096 || group_count < 1 ||
+      experts % group_count != 0 || group_keep < 1 || group_keep > group_count || top > group_keep * (experts / group_count))
+    return DISTIE_ERR_ARG;
   const int warps = kRouteThreads / 32;
-  const size_t shared = (size_t)warps * experts * sizeof(float);
+  const size_t shared = (size_t)warps * (experts + group_count) * sizeof(float);
   if (shared > 48 * 1024) cudaFuncSetAttribute(route_pick_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
   route_pick_kernel<<<(tokens + warps - 1) / warps, kRouteThreads, shared, stream>>>(logits, logit_stride, tokens, experts,
-                                                                                    top, ids, weights);
+                                                                                    top, ids, weights, group_count, group_keep,
+                                                                                    weight_scale);
   DISTIE_LAUNCH_CHECK();
   return 0;
 }

@@ -698,7 +698,7 @@ class DeviceKernels(KernelSet):
         self._ran("stabilized_readout")
         return out
 
-    def route_top(self, x, router, top, scoring="sigmoid"):
+    def route_top(self, x, router, top, scoring="sigmoid", groups=None, weight_scale=1.0, extra_rows=0):
         if scoring != "sigmoid":
             raise KernelError(f"route_top: scoring {scoring!r} is not built; 'sigmoid' is")
         library.load_unit("routed")
@@ -706,27 +706,32 @@ class DeviceKernels(KernelSet):
             x = x.to(router.dtype)  # a router kept in 32-bit reads the activations widened
         if x.stride(1) != 1 or not router.is_contiguous():
             raise KernelError("route_top: rows with unit column stride are expected")
-        tokens, experts = x.shape[0], router.shape[0]
+        extra = int(extra_rows)
+        tokens, experts = x.shape[0], router.shape[0] - extra
+        count, keep = (int(groups[0]), int(groups[1])) if groups is not None else (1, 1)
         ids = torch.empty((tokens, top), dtype=torch.int32, device=x.device)
         weights = torch.empty((tokens, top), dtype=torch.float32, device=x.device)
         if self._tensor_core(x, router):
             # Prompt portions in bfloat16: the logits are a product on the tcgen05 tile kernel (float32 accumulators,
             # stored as float32), and a small kernel picks from them.
-            logits = torch.empty((tokens, experts), dtype=torch.float32, device=x.device)
+            logits = torch.empty((tokens, experts + extra), dtype=torch.float32, device=x.device)
             self._gemm_tcgen05(x, router, logits, 1)
             check(function("distie_route_pick")(logits.data_ptr(), logits.stride(0), tokens, experts, top, ids.data_ptr(),
-                                                weights.data_ptr(), self._stream()), "route_pick")
+                                                weights.data_ptr(), count, keep, float(weight_scale), self._stream()),
+                  "route_pick")
             self._ran("route_top")
-            return ids, weights
+            return (ids, weights, logits[:, experts:]) if extra else (ids, weights)
+        extra_out = torch.empty((tokens, extra), dtype=torch.float32, device=x.device) if extra else None
         check(
             function("distie_route_top")(x.data_ptr(), x.stride(0), router.data_ptr(), tokens, x.shape[1], experts, top,
-                                         ids.data_ptr(), weights.data_ptr(), _CODE[x.dtype], self._stream()),
+                                         ids.data_ptr(), weights.data_ptr(), count, keep, float(weight_scale), extra,
+                                         extra_out.data_ptr() if extra else None, _CODE[x.dtype], self._stream()),
             "route_top",
         )
         self._ran("route_top")
-        return ids, weights
+        return (ids, weights, extra_out) if extra else (ids, weights)
 
-    def routed_swiglu(self, x, ids, weights, gate_up, down, scale_input=True):
+    def routed_swiglu(self, x, ids, weights, gate_up, down, scale_input=True, limit=None):
         if gate_up.dtype != x.dtype or down.dtype != x.dtype:
             if gate_up.dtype != down.dtype:
                 raise KernelError("routed_swiglu: the experts' matrices are of one type")
@@ -739,7 +744,7 @@ class DeviceKernels(KernelSet):
         if code == 1 and (x.stride(0) % 8 or hidden % 8 or ff % 8):
             # rows that are no multiples of 16 bytes: the float32 form of the grouped products takes any size
             x, gate_up, down, code = x.float(), gate_up.float(), down.float(), 0
-        if code == 1 and self.dtype == torch.bfloat16 and tokens * top >= _GROUPED_TENSOR_CORE_PAIRS:
+        if code == 1 and self.dtype == torch.bfloat16 and tokens * top >= _GROUPED_TENSOR_CORE_PAIRS and limit is None:
             return self._routed_swiglu_tcgen05(x, ids, weights, gate_up, down, scale_input)
         tile = function("distie_routed_tile")(code, hidden, ff, tokens * top, experts)
         words = function("distie_route_plan_words")(tokens * top, experts, tile)
@@ -750,7 +755,7 @@ class DeviceKernels(KernelSet):
             function("distie_routed_swiglu")(
                 x.data_ptr(), x.stride(0), ids.data_ptr(), weights.data_ptr(), gate_up.data_ptr(), down.data_ptr(),
                 plan.data_ptr(), mid.data_ptr(), out.data_ptr(), tokens, top, experts, hidden, ff, int(bool(scale_input)),
-                code, self.error_flag.data_ptr(), self._stream(),
+                float(limit) if limit is not None else 0.0, code, self.error_flag.data_ptr(), self._stream(),
             ),
             "routed_swiglu",
         )
@@ -787,6 +792,111 @@ class DeviceKernels(KernelSet):
                                                 int(not scale_input), stream), "routed_scatter")
         self._ran("routed_swiglu", 5)
         self._ran("gemm_tcgen05_grouped", 0)
+        return out
+
+    # -- gated and squared-ReLU hidden layers on float32 accumulators; attention through a latent ------------------
+    def _glu_act(self, x32, ff: int, kind: int, limit, row_gate):
+        library.load_unit("latent")
+        tokens = x32.shape[-2]
+        out = torch.empty((tokens, ff), dtype=self.dtype, device=x32.device)
+        gate = self._sliced(row_gate, "glu_act") if row_gate is not None else (None, 0, 1, 0)
+        check(
+            function("distie_glu_act")(*self._sliced(x32, "glu_act"), tokens, ff, kind, float(limit) if limit is not None else 0.0,
+                                       *gate, out.data_ptr(), out.stride(0), self.code, self._stream()),
+            "glu_act",
+        )
+        self._ran("glu_act")
+        return out
+
+    def linear_glu(self, x, weight, limit=None, row_gate=None):
+        if weight.shape[0] % 2:
+            raise KernelError("linear_glu: gate rows and up rows are stacked, so the weight has an even number of rows")
+        if limit is None and row_gate is None:
+            return self.linear_swiglu(x, weight)
+        if row_gate is not None and row_gate.dim() == 2 and row_gate.shape[-1] != 1:
+            raise KernelError("linear_glu: the row gate is one logit per row")
+        return self._glu_act(self.linear_split(x, weight), weight.shape[0] // 2, 0, limit, row_gate)
+
+    def linear_act(self, x, weight, kind="relu2"):
+        if kind != "relu2":
+            raise KernelError(f"linear_act: activation {kind!r} is not built; 'relu2' is")
+        return self._glu_act(self.linear_split(x, weight), weight.shape[0], 1, None, None)
+
+    def latent_kv_write(self, proj, step, kv, rotary, q_rank, q_norm, kv_rank, kv_norm, rot_dim, eps, q_latent_out) -> None:
+        library.load_unit("latent")
+        write = kv is not None
+        if write and (kv.k.dtype != q_latent_out.dtype or kv.k.shape[-1] != kv_rank + rot_dim or kv.k.shape[-3] != 1
+                      or not kv.k.is_contiguous()):
+            raise KernelError("latent_kv_write: the cache holds one contiguous row [kv_rank + rot_dim] per token, of q's type")
+        table = kv.block_table if write else step.seq_seat
+        turned = rotary.rotary_dim if rotary is not None else 0
+        check(
+            function("distie_latent_kv_write")(
+                *self._sliced(proj, "latent_kv_write"), q_rank, q_norm.data_ptr(), kv_rank,
+                kv_norm.data_ptr() if write else None, rot_dim, float(eps), q_latent_out.data_ptr(), q_latent_out.stride(0),
+                step.positions.data_ptr(), step.token_seq.data_ptr(), step.seq_seat.data_ptr(), table.data_ptr(),
+                table.shape[-1] if write else 1, rotary.inv_freq.data_ptr() if rotary is not None else None,
+                float(rotary.factor) if rotary is not None else 1.0, turned,
+                int(rotary.interleaved) if rotary is not None else 0, kv.k.data_ptr() if write else None,
+                kv.page_size if write else 1, kv.num_pages if write else 1, int(write), step.num_tokens,
+                _CODE[q_latent_out.dtype], self.error_flag.data_ptr(), self._stream(),
+            ),
+            "latent_kv_write",
+        )
+        self._ran("latent_kv_write")
+
+    def latent_queries(self, q, up_keys, step, rotary, num_heads, dim, rot_dim):
+        tokens = step.num_tokens
+        plain = torch.empty((num_heads, tokens, dim), dtype=self.dtype, device=q.device)
+        rotated = torch.empty((tokens, num_heads, rot_dim), dtype=self.dtype, device=q.device)
+        check(
+            function("distie_latent_q_prepare")(
+                *self._sliced(q, "latent_queries"), tokens, num_heads, dim, rot_dim, step.positions.data_ptr(),
+                rotary.inv_freq.data_ptr() if rotary is not None else None,
+                float(rotary.factor) if rotary is not None else 1.0, rotary.rotary_dim if rotary is not None else 0,
+                int(rotary.interleaved) if rotary is not None else 0, plain.data_ptr(), rotated.data_ptr(), self.code,
+                self._stream(),
+            ),
+            "latent_q_prepare",
+        )
+        self._ran("latent_q_prepare")
+        # per head [T, dim] x [dim, kv_rank]: a batched library product (float32 accumulation; FMA-only in the float32 set)
+        return torch.bmm(plain, up_keys), rotated
+
+    def latent_attention(self, folded, rotated, step, kv, num_heads, kv_rank, rot_dim, scale, sink, out) -> None:
+        if kv.k.dtype != folded.dtype or not folded.is_contiguous() or not rotated.is_contiguous() or not out.is_contiguous():
+            raise KernelError("latent_attention: contiguous queries and output of the cache's type are expected")
+        tokens = step.num_tokens
+        # Steps of few tokens over long requests: the keys are split so that the machine is filled.
+        blocks = tokens * -(-num_heads // 4)
+        splits = max(1, min(-(-2 * self.sm_count // max(blocks, 1)), -(-max(int(step.max_kv_len), 1) // 128), 64))
+        partial = None
+        if splits > 1:
+            floats = function("distie_latent_attention_scratch_floats")(tokens, num_heads, kv_rank, splits)
+            partial = torch.empty(floats, dtype=torch.float32, device=folded.device)
+        check(
+            function("distie_latent_attention")(
+                folded.data_ptr(), rotated.data_ptr(), out.data_ptr(), partial.data_ptr() if partial is not None else None,
+                tokens, num_heads, kv_rank, rot_dim, step.positions.data_ptr(), step.token_seq.data_ptr(),
+                step.seq_seat.data_ptr(), kv.block_table.data_ptr(), kv.block_table.shape[-1], kv.k.data_ptr(),
+                kv.page_size, kv.num_pages, float(scale), sink.data_ptr() if sink is not None else None, splits,
+                _CODE[folded.dtype], self.error_flag.data_ptr(), self._stream(),
+            ),
+            "latent_attention",
+        )
+        self._ran("latent_attention", 2 if splits > 1 else 1)
+
+    def latent_values(self, mixed, up_values, gate, num_heads, value_dim):
+        tokens = mixed.shape[1]
+        per_head = torch.bmm(mixed, up_values)  # [heads, T, value_dim] in the set's dtype
+        out = torch.empty((tokens, num_heads * value_dim), dtype=self.dtype, device=mixed.device)
+        g = self._sliced(gate, "latent_values") if gate is not None else (None, 0, 1, 0)
+        check(
+            function("distie_latent_gate")(per_head.data_ptr(), tokens, num_heads, value_dim, *g, out.data_ptr(),
+                                           out.stride(0), self.code, self._stream()),
+            "latent_gate",
+        )
+        self._ran("latent_gate")
         return out
 
     def sample(self, logits, temperatures, uniforms, out_tokens) -> None:

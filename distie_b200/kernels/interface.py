@@ -14,7 +14,8 @@ Shapes (``T`` tokens of this step, ``B`` requests of this step):
     seq_seat [B] (seat = row of the block tables and of the state slots).
 ``KvSlot``        one cache slot of one group
     k  [pages, kv_heads, page_size, head_dim], v  [pages, kv_heads, page_size, value_dim];
-    block_table [seats, width] int32
+    block_table [seats, width] int32.  In a group whose values lie inside its keys (attention through
+    a latent) ``v`` is a view of the first ``value_dim`` columns of ``k``.
 
 Which keys a token sees: all keys up to its own position (``first_visible``), the last
 ``window`` of them, or those of its own ``chunk`` (positions ``chunk * n .. chunk * (n + 1) - 1``);
@@ -246,17 +247,73 @@ class KernelSet(ABC):
         ``max(|n . q|, floor[t, h]) + 1e-6``."""
         raise NotImplementedError
 
-    def route_top(self, x, router, top: int, scoring: str = "sigmoid"):
+    def route_top(self, x, router, top: int, scoring: str = "sigmoid", groups: tuple[int, int] | None = None,
+                  weight_scale: float = 1.0, extra_rows: int = 0):
         """The ``top`` experts of every token: logits ``x @ router.T`` (``router [experts, hidden]``) accumulated in
         float32 -> ``(ids [T, top] int32, weights [T, top] float32)``, ``weights`` the chosen experts' scores
-        (``sigmoid(logit)``, not renormalised), the largest first, ties to the lower index."""
+        (``sigmoid(logit)``, not renormalised) times ``weight_scale``, the largest first, ties to the lower index.
+
+        ``groups = (count, keep)``: the experts form ``count`` equal groups of neighbours; a group's score is the
+        sum of its two largest scores (of its one score, for groups of one), and only experts of the ``keep`` groups
+        with the largest scores (ties to the lower group) can be chosen.  With ``extra_rows`` the router matrix has
+        that many more rows below the experts', which are no experts: their float32 logits ``[T, extra_rows]`` are
+        returned as a third value (a gate that reads the same input, made in the same pass)."""
         raise NotImplementedError
 
-    def routed_swiglu(self, x, ids, weights, gate_up, down, scale_input: bool = True):
+    def routed_swiglu(self, x, ids, weights, gate_up, down, scale_input: bool = True, limit: float | None = None):
         """Every token through its chosen experts: ``gate_up [experts, 2 ff, hidden]`` (gate rows, then up rows),
         ``down [experts, hidden, ff]``; expert e of pair (t, j) computes ``down_e (silu(gate_e z) * (up_e z))`` with
-        ``z = weights[t, j] * x[t]`` (``scale_input``) or on ``x[t]`` with the result times the weight.  Returns
+        ``z = weights[t, j] * x[t]`` (``scale_input``) or on ``x[t]`` with the result times the weight.  With a
+        ``limit`` the hidden activation is the capped form of :meth:`linear_glu`.  Returns
         float32 slices ``[top, T, hidden]`` whose sum over the first axis is the routed output."""
+        raise NotImplementedError
+
+    def linear_glu(self, x, weight, limit: float | None = None, row_gate=None):
+        """A gated hidden layer: ``weight = [Wg; Wu]`` stacked along the rows, ``g = x Wg^T``, ``u = x Wu^T``
+        (float32 accumulators).  ``limit`` None: ``silu(g) * u``; a number: the capped form
+        ``g' = min(g, limit)``, ``u' = clamp(u, -limit, limit)``, ``g' * sigmoid(1.702 g') * (u' + 1)``.
+        ``row_gate`` (float32 ``[T]`` logits, any stride, or slices ``[S, T]``): row t also times
+        ``sigmoid(row_gate[t])``.  Returns ``[T, rows / 2]`` in the set's dtype."""
+        raise NotImplementedError
+
+    def linear_act(self, x, weight, kind: str = "relu2"):
+        """``act(x @ weight.T)`` in the set's dtype, the activation applied to the float32 accumulators:
+        ``"relu2"`` is ``max(z, 0)^2``."""
+        raise NotImplementedError
+
+    # -- attention through a latent: one shared key/value row per token, queries folded into the latent's space ------
+    def latent_kv_write(self, proj, step: StepTensors, kv: KvSlot | None, rotary: RotaryTable | None, q_rank: int,
+                        q_norm, kv_rank: int, kv_norm, rot_dim: int, eps: float, q_latent_out) -> None:
+        """``proj`` is the float32 projection ``[T, q_rank (+ kv_rank + rot_dim)]`` (or its slices).  Columns
+        ``[0, q_rank)`` divided by their root mean square (``eps`` inside the root) times ``q_norm`` go to
+        ``q_latent_out [T, q_rank]`` in the set's dtype.  With ``kv`` the next ``kv_rank`` columns, normed the same
+        way with ``kv_norm``, and the last ``rot_dim`` columns, rotated by ``rotary`` at the token's position and not
+        normed, are stored side by side as the token's one row ``[kv_rank + rot_dim]`` of ``kv.k``.  All float32
+        up to the stores.  Without ``kv`` the projection has the query columns only."""
+        raise NotImplementedError
+
+    def latent_queries(self, q, up_keys, step: StepTensors, rotary: RotaryTable | None, num_heads: int, dim: int,
+                       rot_dim: int):
+        """``q`` is the float32 query projection ``[T, heads * (dim + rot_dim)]`` (or its slices), per head ``dim``
+        plain columns and ``rot_dim`` columns to rotate; ``up_keys [heads, dim, kv_rank]`` maps a latent to a
+        head's plain key.  Returns ``(folded [heads, T, kv_rank], rotated [T, heads, rot_dim])`` in the set's
+        dtype: ``folded[h, t] = q_plain[t, h] @ up_keys[h]`` (so that ``folded . latent == q_plain . key``)."""
+        raise NotImplementedError
+
+    def latent_attention(self, folded, rotated, step: StepTensors, kv: KvSlot, num_heads: int, kv_rank: int,
+                         rot_dim: int, scale: float, sink, out) -> None:
+        """Causal softmax attention of every token over its request's rows ``[latent | rotated key part]`` of
+        ``kv.k``, shared by all heads: score ``(folded[h, t] . latent_j + rotated[t, h] . part_j) * scale`` for every
+        ``j <= position``; with ``sink [heads]`` (float32) the denominator also holds ``exp(sink_h)``;
+        ``out[h, t] = sum_j weight_j latent_j`` (``[heads, T, kv_rank]``, the set's dtype).  Scores, softmax and the
+        sum are float32."""
+        raise NotImplementedError
+
+    def latent_values(self, mixed, up_values, gate, num_heads: int, value_dim: int):
+        """``mixed [heads, T, kv_rank]`` (what :meth:`latent_attention` left), ``up_values [heads, kv_rank,
+        value_dim]`` -> ``[T, heads * value_dim]`` in the set's dtype: head h of token t is ``mixed[h, t] @
+        up_values[h]`` times ``sigmoid(gate[t, h])`` (``gate`` float32 ``[T, heads]``, any stride, or slices; None:
+        no gate)."""
         raise NotImplementedError
 
     # -- layer norm, gates, short convolutions and linear recurrences (layers with per-request state) --------

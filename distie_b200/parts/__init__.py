@@ -16,7 +16,7 @@ from .base import (
     TensorSpec,
     build_part,
 )
-from . import attention, block, hybrid, memory, mlp, norm, position, recurrent, routed  # noqa: F401  (register the built-in kinds)
+from . import attention, block, hybrid, latent, memory, mlp, norm, position, recurrent, routed  # noqa: F401  (register the built-in kinds)
 
 __all__ = [
     "BLOCKS",

@@ -62,10 +62,16 @@ class CacheNeed:
     chunk: int | None = None   # n: a token reads only keys of its own chunk of n positions (counted from 0)
     value_dim: int | None = None  # size of a value when it differs from head_dim
     keep_first: int = 0        # beside a window: the request's first n positions stay readable for good
+    values_in_keys: bool = False  # a value is the first value_dim columns of its key's row: nothing is stored twice
 
     @property
     def v_dim(self) -> int:
         return int(self.value_dim or self.head_dim)
+
+    @property
+    def row_elements(self) -> int:
+        """Elements one token holds per kv head in a slot of this group."""
+        return self.head_dim if self.values_in_keys else self.head_dim + self.v_dim
 
 
 @dataclass(frozen=True)

@@ -1,4 +1,4 @@
-"""SwiGLU feed-forward, dense: ``down(silu(gate(x)) * up(x))``, no biases.
+"""Dense feed-forwards, no biases: SwiGLU ``down(silu(gate(x)) * up(x))`` and ``activated`` ``down(act(up(x)))``.
 
 Formula of the reference (worker/src/inference/qwen2/model.py:228-236).  Gate and
 up are one product against the row-stacked weight ``[2 * inter, hidden]``.
@@ -52,6 +52,41 @@ class SwiGluFeedForward:
     def forward(self, x: torch.Tensor, run: LayerRun) -> torch.Tensor:
         # The down product's float32 slices are summed by the norm that follows (or by the stream).
         return self.kernels.linear_split(self.kernels.linear_swiglu(x, self.gate_up.weight), self.down.weight)
+
+
+@FEED_FORWARDS.register("activated")
+class ActivatedFeedForward:
+    """``down(act(up(x)))`` with the activation on the product's float32 accumulators.  params:
+    ``intermediate_size``, ``activation`` (``"relu2"``: the square of ReLU); optional ``names``: what the names of
+    the up and down matrices add to the prefix (default ``up_proj.weight``, ``down_proj.weight``)."""
+
+    _NAMES = ("up_proj.weight", "down_proj.weight")
+    _ACTIVATIONS = ("relu2",)
+
+    def __init__(self, up: torch.Tensor, down: torch.Tensor, activation: str, kernels) -> None:
+        self.up, self.down, self.activation, self.kernels = up, down, activation, kernels
+
+    @classmethod
+    def _check(cls, spec: PartSpec) -> None:
+        if spec.params.get("activation") not in cls._ACTIVATIONS:
+            raise ValueError(f"activation {spec.params.get('activation')!r}: one of {cls._ACTIVATIONS}")
+
+    @classmethod
+    def tensor_specs(cls, spec: PartSpec, hidden_size: int) -> list[TensorSpec]:
+        cls._check(spec)
+        p, inter = spec.prefix, int(spec.params["intermediate_size"])
+        up, down = spec.params.get("names", cls._NAMES)
+        return [TensorSpec(p + up, (inter, hidden_size)), TensorSpec(p + down, (hidden_size, inter))]
+
+    @classmethod
+    def build(cls, spec: PartSpec, ctx: BuildContext) -> "ActivatedFeedForward":
+        cls._check(spec)
+        p, w = spec.prefix, ctx.weights
+        up, down = spec.params.get("names", cls._NAMES)
+        return cls(w.matrix(p + up), w.matrix(p + down), spec.params["activation"], ctx.kernels)
+
+    def forward(self, x: torch.Tensor, run: LayerRun) -> torch.Tensor:
+        return self.kernels.linear_split(self.kernels.linear_act(x, self.up, self.activation), self.down)
 
 
 @FEED_FORWARDS.register("none")

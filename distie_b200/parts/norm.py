@@ -18,8 +18,9 @@ from .base import NORMS, BuildContext, TensorSpec
 
 @NORMS.register("rmsnorm")
 class RMSNorm:
-    """params: ``eps``; optional ``name`` (what the tensor's name adds to the prefix, default ``"weight"``) and
-    ``offset`` (added to the stored scale; 0 when the checkpoint stores the scale itself).
+    """params: ``eps``; optional ``name`` (what the tensor's name adds to the prefix, default ``"weight"``),
+    ``offset`` (added to the stored scale; 0 when the checkpoint stores the scale itself) and ``exact`` (the norm
+    is float32 up to the one cast of its output, scale included; an offset implies it).
     tensors: ``<prefix><name> [hidden]``."""
 
     def __init__(self, weight, eps: float, kernels, exact: bool = False) -> None:
@@ -39,7 +40,7 @@ class RMSNorm:
         offset = float(spec.params.get("offset", 0.0))
         if offset:
             weight = weight + offset  # float32: exact for a scale stored in 16 bits, up to float32 rounding
-        return cls(weight, spec.params["eps"], ctx.kernels, exact=bool(offset))
+        return cls(weight, spec.params["eps"], ctx.kernels, exact=bool(offset) or bool(spec.params.get("exact")))
 
     def pending(self, value) -> Normed:
         """``value`` (a sublayer's output) as something the next norm adds to the residual through this norm."""

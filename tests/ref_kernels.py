@@ -331,13 +331,34 @@ def stabilized_readout(read, floor, heads, value_dim):
     return (parts[:, :, :value_dim] / (lower[:, :, None] + 1e-6)).reshape(tokens, heads * value_dim)
 
 
-def route_top(x, router, top, scoring="sigmoid"):
-    scores = torch.sigmoid(x.float() @ router.float().T)
-    weights, ids = torch.sort(scores, dim=-1, descending=True, stable=True)
-    return ids[:, :top].to(torch.int32).contiguous(), weights[:, :top].contiguous()
+def glu(g, u, limit=None):
+    """The hidden activation of a gated layer, float32: SwiGLU, or with a ``limit`` the capped form."""
+    if limit is None:
+        return _silu(g) * u
+    g = torch.clamp(g, max=float(limit))
+    u = torch.clamp(u, -float(limit), float(limit))
+    return g * torch.sigmoid(1.702 * g) * (u + 1.0)
 
 
-def routed_swiglu(x, ids, weights, gate_up, down, scale_input=True):
+def route_top(x, router, top, scoring="sigmoid", groups=None, weight_scale=1.0, extra_rows=0):
+    logits = x.float() @ router.float().T
+    experts = router.shape[0] - int(extra_rows)
+    scores = torch.sigmoid(logits[:, :experts])
+    allowed = scores.clone()
+    if groups is not None and groups[0] > 1 and groups[1] < groups[0]:
+        count, keep = int(groups[0]), int(groups[1])
+        size = experts // count
+        members = scores.reshape(-1, count, size)
+        group_score = torch.sort(members, dim=-1, descending=True).values[..., :2].sum(-1)
+        kept = torch.sort(group_score, dim=-1, descending=True, stable=True).indices[:, :keep]
+        mask = torch.zeros_like(group_score, dtype=torch.bool).scatter_(1, kept, True)
+        allowed = torch.where(mask[:, :, None].expand_as(members).reshape(-1, experts), scores, torch.full_like(scores, -1.0))
+    weights, ids = torch.sort(allowed, dim=-1, descending=True, stable=True)
+    out = ids[:, :top].to(torch.int32).contiguous(), (weights[:, :top] * float(weight_scale)).contiguous()
+    return out if not extra_rows else (*out, logits[:, experts:].contiguous())
+
+
+def routed_swiglu(x, ids, weights, gate_up, down, scale_input=True, limit=None):
     tokens, top = ids.shape
     ff = gate_up.shape[1] // 2
     out = torch.zeros((top, tokens, x.shape[1]), dtype=torch.float32, device=x.device)
@@ -346,10 +367,84 @@ def routed_swiglu(x, ids, weights, gate_up, down, scale_input=True):
             e, w = int(ids[t, j]), weights[t, j].float()
             z = (x[t].float() * w).to(x.dtype).float() if scale_input else x[t].float()
             both = gate_up[e].float() @ z
-            hidden = (_silu(both[:ff]) * both[ff:]).to(x.dtype).float()
+            hidden = glu(both[:ff], both[ff:], limit).to(x.dtype).float()
             y = down[e].float() @ hidden
             out[j, t] = y if scale_input else y * w
     return out
+
+
+def linear_glu(x, weight, dtype, limit=None, row_gate=None):
+    both = x.float() @ weight.float().T
+    ff = weight.shape[0] // 2
+    hidden = glu(both[:, :ff], both[:, ff:], limit)
+    if row_gate is not None:
+        gate = whole(row_gate) if row_gate.dim() == 3 else row_gate.float()
+        hidden = hidden * torch.sigmoid(gate.reshape(-1))[:, None]
+    return hidden.to(dtype)
+
+
+def linear_act(x, weight, dtype, kind="relu2"):
+    z = x.float() @ weight.float().T
+    if kind != "relu2":
+        raise ValueError(kind)
+    return (torch.relu(z) ** 2).to(dtype)
+
+
+# -- attention through a latent ------------------------------------------------------------------------------------
+def _unit_rms(x, weight, eps):
+    return x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * weight.float()
+
+
+def latent_kv_write(proj, step: StepTensors, kv, rotary, q_rank, q_norm, kv_rank, kv_norm, rot_dim, eps, dtype):
+    """Returns the normed query latent ``[T, q_rank]``; stores the token's row in ``kv.k`` (if ``kv``)."""
+    tokens = step.num_tokens
+    proj = whole(proj)[:tokens]
+    q_latent = _unit_rms(proj[:, :q_rank], q_norm, eps).to(dtype)
+    if kv is not None:
+        latent = _unit_rms(proj[:, q_rank : q_rank + kv_rank], kv_norm, eps)
+        part = proj[:, q_rank + kv_rank : q_rank + kv_rank + rot_dim]
+        part = rotate(part[:, None, :], step.positions[:tokens], rotary)[:, 0]
+        pos = step.positions[:tokens].long()
+        pages = kv.block_table[token_seats(step), pos // kv.page_size].long()
+        if bool(((pages < 0) | (pages >= kv.num_pages)).any()):
+            raise IndexError("a new token's page is missing from its block table")
+        kv.k[pages, 0, pos % kv.page_size, :] = torch.cat([latent, part], dim=-1).to(kv.k.dtype)
+    return q_latent
+
+
+def latent_queries(q, up_keys, step: StepTensors, rotary, num_heads, dim, rot_dim, dtype):
+    tokens = step.num_tokens
+    q = whole(q)[:tokens].reshape(tokens, num_heads, dim + rot_dim)
+    rotated = rotate(q[..., dim:], step.positions[:tokens], rotary).to(dtype)
+    plain = q[..., :dim].to(dtype).float()
+    folded = torch.einsum("thd,hdr->htr", plain, up_keys.float()).to(dtype)
+    return folded.contiguous(), rotated.contiguous()
+
+
+def latent_attention(folded, rotated, step: StepTensors, kv: KvSlot, num_heads, kv_rank, rot_dim, scale, sink):
+    tokens = step.num_tokens
+    out = torch.zeros((num_heads, tokens, kv_rank), dtype=folded.dtype, device=folded.device)
+    for t in range(tokens):
+        pos = int(step.positions[t])
+        seat = int(step.seq_seat[int(step.token_seq[t])])
+        keys = torch.arange(0, pos + 1, device=folded.device)
+        pages = kv.block_table[seat, keys // kv.page_size].long()
+        if bool(((pages < 0) | (pages >= kv.num_pages)).any()):
+            raise IndexError("a block table does not cover the keys a token attends to")
+        rows = kv.k[pages, 0, keys % kv.page_size, :].float()  # [n, kv_rank + rot_dim]
+        scores = (folded[:, t].float() @ rows[:, :kv_rank].T + rotated[t].float() @ rows[:, kv_rank:].T) * scale  # [H, n]
+        if sink is not None:
+            scores = torch.cat([scores, sink.float()[:, None]], dim=1)
+        probs = torch.softmax(scores, dim=-1)[:, : pos + 1]
+        out[:, t] = (probs @ rows[:, :kv_rank]).to(folded.dtype)
+    return out
+
+
+def latent_values(mixed, up_values, gate, num_heads, value_dim, dtype):
+    out = torch.einsum("htr,hrv->thv", mixed.float(), up_values.float())
+    if gate is not None:
+        out = out.to(dtype).float() * torch.sigmoid(whole(gate) if gate.dim() == 3 else gate.float())[:, :, None]
+    return out.reshape(out.shape[0], num_heads * value_dim).to(dtype)
 
 
 def sample(logits, temperatures, uniforms):
@@ -417,11 +512,29 @@ class RefKernels(KernelSet):
     def stabilized_readout(self, read, floor, heads, value_dim):
         return stabilized_readout(read, floor, heads, value_dim)
 
-    def route_top(self, x, router, top, scoring="sigmoid"):
-        return route_top(x, router, top, scoring)
+    def route_top(self, x, router, top, scoring="sigmoid", groups=None, weight_scale=1.0, extra_rows=0):
+        return route_top(x, router, top, scoring, groups, weight_scale, extra_rows)
 
-    def routed_swiglu(self, x, ids, weights, gate_up, down, scale_input=True):
-        return routed_swiglu(x, ids, weights, gate_up, down, scale_input)
+    def routed_swiglu(self, x, ids, weights, gate_up, down, scale_input=True, limit=None):
+        return routed_swiglu(x, ids, weights, gate_up, down, scale_input, limit)
+
+    def linear_glu(self, x, weight, limit=None, row_gate=None):
+        return linear_glu(x, weight, self.dtype, limit, row_gate)
+
+    def linear_act(self, x, weight, kind="relu2"):
+        return linear_act(x, weight, self.dtype, kind)
+
+    def latent_kv_write(self, proj, step, kv, rotary, q_rank, q_norm, kv_rank, kv_norm, rot_dim, eps, q_latent_out):
+        q_latent_out.copy_(latent_kv_write(proj, step, kv, rotary, q_rank, q_norm, kv_rank, kv_norm, rot_dim, eps, self.dtype))
+
+    def latent_queries(self, q, up_keys, step, rotary, num_heads, dim, rot_dim):
+        return latent_queries(q, up_keys, step, rotary, num_heads, dim, rot_dim, self.dtype)
+
+    def latent_attention(self, folded, rotated, step, kv, num_heads, kv_rank, rot_dim, scale, sink, out):
+        out.copy_(latent_attention(folded, rotated, step, kv, num_heads, kv_rank, rot_dim, scale, sink))
+
+    def latent_values(self, mixed, up_values, gate, num_heads, value_dim):
+        return latent_values(mixed, up_values, gate, num_heads, value_dim, self.dtype)
 
     def add_layernorm(self, delta, residual, weight, bias, eps, out, rows_index=None):
         new_residual, normed = add_layernorm(delta, residual, weight, bias, eps, self.dtype, rows_index)
