@@ -26,7 +26,8 @@ from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Branches, BuildContext, 
 
 @BLOCKS.register("pre_norm")
 class PreNormBlock:
-    """norms: ``input`` (before the mixer) and ``post_mixer`` (before the feed-forward)."""
+    """norms: ``input`` (before the mixer) and ``post_mixer`` (before the feed-forward).  A layer whose feed-forward
+    is of kind ``none`` may leave ``post_mixer`` out: the mixer's output then stays pending for the next norm."""
 
     def __init__(self, norm_in, mixer, norm_post, feed_forward, dtype) -> None:
         self.norm_in = norm_in
@@ -45,16 +46,19 @@ class PreNormBlock:
         return (
             NORMS.get(layer.norms["input"].kind).tensor_specs(layer.norms["input"], hidden_size)
             + MIXERS.get(layer.mixer.kind).tensor_specs(layer.mixer, hidden_size)
-            + NORMS.get(layer.norms["post_mixer"].kind).tensor_specs(layer.norms["post_mixer"], hidden_size)
+            + (NORMS.get(layer.norms["post_mixer"].kind).tensor_specs(layer.norms["post_mixer"], hidden_size)
+               if "post_mixer" in layer.norms else [])
             + FEED_FORWARDS.get(layer.feed_forward.kind).tensor_specs(layer.feed_forward, hidden_size)
         )
 
     @classmethod
     def build(cls, layer: LayerSpec, ctx: BuildContext) -> "PreNormBlock":
+        if "post_mixer" not in layer.norms and layer.feed_forward.kind != "none":
+            raise ValueError("a pre_norm layer with a feed-forward needs the norm 'post_mixer'")
         return cls(
             build_part(NORMS, layer.norms["input"], ctx),
             build_part(MIXERS, layer.mixer, ctx),
-            build_part(NORMS, layer.norms["post_mixer"], ctx),
+            build_part(NORMS, layer.norms["post_mixer"], ctx) if "post_mixer" in layer.norms else None,
             build_part(FEED_FORWARDS, layer.feed_forward, ctx),
             ctx.dtype,
         )
@@ -64,6 +68,9 @@ class PreNormBlock:
         x = torch.empty(residual.shape, dtype=self.dtype, device=residual.device)
         self.norm_in.apply(stream.pending, residual, x)
         mixed = self.mixer.forward(x, run)
+        if self.norm_post is None:  # no feed-forward: the next norm adds the mixer's output to the residual
+            stream.pending = mixed
+            return
         self.norm_post.apply(mixed, residual, x)
         stream.pending = self.feed_forward.forward(x, run)
 

@@ -124,10 +124,29 @@ def choose_experts(scores, top, group_count, group_keep):
     return sorted(allowed, key=lambda e: (-float(scores[e]), e))[:top]
 
 
-def routed_ff(h, w, p, mlp):
+def choice_margin(scores, top, group_count, group_keep):
+    """How far the choice is from another one: the smallest gap, in scores, between what was taken last and what was
+    left out first, among the groups and among the eligible experts (infinite when nothing was left out)."""
+    experts = scores.shape[0]
+    size = experts // group_count
+    gaps = []
+    group_score = [sum(sorted((float(s) for s in scores[g * size : (g + 1) * size]), reverse=True)[:2]) for g in range(group_count)]
+    ranked = sorted(range(group_count), key=lambda g: (-group_score[g], g))
+    if group_keep < group_count:
+        gaps.append(group_score[ranked[group_keep - 1]] - group_score[ranked[group_keep]])
+    allowed = sorted((float(scores[e]) for e in range(experts) if e // size in ranked[:group_keep]), reverse=True)
+    if top < len(allowed):
+        gaps.append(allowed[top - 1] - allowed[top])
+    return min(gaps) if gaps else float("inf")
+
+
+def routed_ff(h, w, p, mlp, margins=None):
     router, groups = mlp["router"], mlp["router"]["groups"]
     scores = torch.sigmoid((h @ w[p + "router"].T).to(torch.float32)).to(h.dtype)
     out = torch.zeros_like(h)
+    if margins is not None:
+        margins.append(torch.tensor([choice_margin(scores[t], int(router["top"]), int(groups["count"]), int(groups["keep"]))
+                                     for t in range(h.shape[0])], dtype=torch.float64))
     for t in range(h.shape[0]):
         for e in choose_experts(scores[t], int(router["top"]), int(groups["count"]), int(groups["keep"])):
             out[t] += float(router["scale"]) * scores[t, e] * capped_expert(h[t : t + 1], w, f"{p}e{e}.", float(mlp["expert"]["limit"]))[0]
@@ -137,18 +156,18 @@ def routed_ff(h, w, p, mlp):
     return out
 
 
-def feed_forward(h, w, p, mlp):
+def feed_forward(h, w, p, mlp, margins=None):
     if mlp["kind"] == "dense":
         return dense_ff(h, w, p)
     if mlp["kind"] == "moe":
-        return routed_ff(h, w, p, mlp)
+        return routed_ff(h, w, p, mlp, margins)
     raise ValueError(mlp["kind"])
 
 
 # -- the model -----------------------------------------------------------------------------------------------------
-def forward(ids, w, cfg, dtype=torch.float64, layer_outputs=None):
+def forward(ids, w, cfg, dtype=torch.float64, layer_outputs=None, margins=None):
     """Logits ``[T, vocab]`` of one sequence from its first token; ``layer_outputs`` (a list) receives the residual
-    stream after every layer."""
+    stream after every layer, ``margins`` (a list) every router's :func:`choice_margin` per token."""
     w = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in w.items()}
     eps = float(cfg["norm"]["eps"])
     positions = torch.arange(len(ids))
@@ -164,7 +183,7 @@ def forward(ids, w, cfg, dtype=torch.float64, layer_outputs=None):
         latent, shared = held[i if m.get("kv_from") is None else int(m["kv_from"])]
         x = x + latent_attention(h, w, p + "mix.", m, eps, positions, latent, shared)
         if layer.get("mlp") is not None:
-            x = x + feed_forward(stored(rms_norm(x, w[p + "norm2"], eps)), w, p + "mlp.", layer["mlp"])
+            x = x + feed_forward(stored(rms_norm(x, w[p + "norm2"], eps)), w, p + "mlp.", layer["mlp"], margins)
         if layer_outputs is not None:
             layer_outputs.append(x.clone())
     return stored(rms_norm(x, w["final.norm"], eps)) @ w["head"].T
@@ -175,4 +194,51 @@ def logit_scale(logits: torch.Tensor) -> float:
     return float(centred.pow(2).mean().sqrt())
 
 
-_ = math  # (kept for callers that build configurations with it)
+# -- the checkpoint of a configuration -----------------------------------------------------------------------------
+def tensor_shapes(cfg) -> dict:
+    width, shapes = cfg["width"], {"embed": (cfg["vocab"], cfg["width"]), "final.norm": (cfg["width"],), "head": (cfg["vocab"], cfg["width"])}
+    for i, layer in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", layer["mixer"]
+        heads, dim, rot, vdim, rank, q_rank = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"], m["q_rank"]
+        shapes[p + "norm1"] = (width,)
+        shapes.update({p + "mix.dq": (q_rank, width), p + "mix.dq.norm": (q_rank,), p + "mix.uq": (heads * (dim + rot), q_rank),
+                       p + "mix.uk": (heads * dim, rank), p + "mix.uv": (heads * vdim, rank), p + "mix.sink": (heads,),
+                       p + "mix.g": (heads, width), p + "mix.o": (width, heads * vdim)})
+        if m.get("kv_from") is None:
+            shapes.update({p + "mix.dkv": (rank + rot, width), p + "mix.dkv.norm": (rank,)})
+        mlp = layer.get("mlp")
+        if mlp is None:
+            continue
+        shapes[p + "norm2"] = (width,)
+        if mlp["kind"] == "dense":
+            shapes.update({p + "mlp.up": (mlp["ff"], width), p + "mlp.down": (width, mlp["ff"])})
+            continue
+        shapes[p + "mlp.router"] = (mlp["router"]["experts"], width)
+        for e in range(mlp["router"]["experts"]):
+            ff = mlp["expert"]["ff"]
+            shapes.update({f"{p}mlp.e{e}.gate": (ff, width), f"{p}mlp.e{e}.up": (ff, width), f"{p}mlp.e{e}.down": (width, ff)})
+        if mlp.get("shared") is not None:
+            ff = mlp["shared"]["ff"]
+            shapes.update({p + "mlp.shared.gate": (ff, width), p + "mlp.shared.up": (ff, width),
+                           p + "mlp.shared.down": (width, ff), p + "mlp.shared.sg": (1, width)})
+    return shapes
+
+
+def random_weights(cfg, seed: int) -> dict:
+    """Weights as a bfloat16 checkpoint holds them (float32 tensors of bfloat16 values): matrices around
+    ``in ** -0.5`` (query and key maps larger, so that scores spread over several units and the softmax is not flat),
+    norm scales around one, sinks of a few units either way, the embedding divided by the configuration's scale."""
+    g = torch.Generator().manual_seed(seed)
+    out = {}
+    for name, shape in tensor_shapes(cfg).items():
+        if name.endswith("norm") or name.endswith("norm1") or name.endswith("norm2"):
+            t = 1.0 + 0.2 * torch.randn(shape, generator=g)
+        elif name.endswith(".sink"):
+            t = 1.5 * torch.randn(shape, generator=g)
+        elif name == "embed":
+            t = torch.randn(shape, generator=g) / float(cfg["embedding"]["scale"])
+        else:
+            gain = 2.5 if name.endswith((".uq", ".uk", ".dkv")) else (2.0 if name.endswith((".router", ".sg", ".g")) else 1.0)
+            t = torch.randn(shape, generator=g) * gain * shape[-1] ** -0.5
+        out[name] = t.to(torch.bfloat16).float()
+    return out
