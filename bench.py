@@ -256,6 +256,28 @@ def fovudra_config(size: dict, layers: int, window: int) -> dict:
             "layers": [pattern[i % 4] for i in range(layers)]}
 
 
+def zururax_config(size: dict, layers: int) -> dict:
+    """The Zururax design at a Qwen2.5 layer's width and head count: heads of 128 plain and 64 rotated dimensions,
+    values of 128, a key/value latent of 512 and a query latent of half the width; every second layer reads the
+    latent of the layer before it; a routed feed-forward whose active part equals the dense one (16 capped experts
+    of a quarter of the dense width in four groups of which two are kept, three per token beside a gated shared
+    one of the same size); the first layer of every four has the dense squared-ReLU feed-forward."""
+    heads, quarter = size["heads"], size["ff"] // 4
+    moe = {"kind": "moe", "router": {"experts": 16, "top": 3, "scale": 2.5, "groups": {"count": 4, "keep": 2}},
+           "expert": {"ff": quarter, "limit": 7.0}, "shared": {"ff": quarter, "limit": 7.0}}
+    dense = {"kind": "dense", "ff": size["ff"]}
+
+    def layer(index: int) -> dict:
+        mixer = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "q_rank": size["width"] // 2,
+                 "scale": 192 ** -0.5, "rot": {"base": 1e6, "dims": 64}}
+        if index % 2:
+            mixer["kv_from"] = index - 1
+        return {"type": "latent_attention", "mixer": mixer, "mlp": dense if index % 4 == 0 else moe}
+
+    return {"architecture": "Zururax", "vocab": COMPARE_VOCAB, "width": size["width"], "norm": {"eps": 1e-6},
+            "embedding": {"scale": 1.0}, "layers": [layer(i) for i in range(layers)]}
+
+
 def qwen2_config(size: dict, layers: int) -> dict:
     return {"architectures": ["Qwen2ForCausalLM"], "vocab_size": COMPARE_VOCAB, "hidden_size": size["width"],
             "intermediate_size": size["ff"], "num_hidden_layers": layers, "num_attention_heads": size["heads"],
@@ -264,9 +286,9 @@ def qwen2_config(size: dict, layers: int) -> dict:
 
 
 def compare_designs(args) -> int:
-    """``--compare zelasun`` (or ``fovudra``): prefill of 2,048 tokens and decode steps at batch ``--batch`` behind
+    """``--compare zelasun`` (or ``fovudra``, ``zururax``): prefill of 2,048 tokens and decode steps at batch ``--batch`` behind
     1,024-token prompts, for the named design beside the Qwen2 decoder (and, for Fovudra, beside Zelasun, the other
-    design with recurrences) at equal width, feed-forward, heads and depth.  Each model is
+    design with recurrences; for Zururax, beside Fovudra, the other design with routed experts) at equal width, feed-forward, heads and depth.  Each model is
     built at two depths (4 and 8 layers) so that the time of a layer is the difference, free of embedding and head.
     One JSON line; not the repository's headline metric."""
     import gc
@@ -280,11 +302,13 @@ def compare_designs(args) -> int:
         names = [args.only_size]
     dtype = "bfloat16" if args.dtype == "bf16" else "float32"
     depths = (4, 8) if args.layers is None else (args.layers,)
-    designs = ("zelasun", "qwen2") if args.compare == "zelasun" else ("fovudra", "zelasun", "qwen2")
+    designs = {"zelasun": ("zelasun", "qwen2"), "fovudra": ("fovudra", "zelasun", "qwen2"),
+               "zururax": ("zururax", "fovudra", "qwen2")}[args.compare]
     if args.designs:
         designs = tuple(d for d in designs if d in args.designs.split(","))
     configs = {"zelasun": lambda size, depth: zelasun_config(size, depth, args.chunk),
                "fovudra": lambda size, depth: fovudra_config(size, depth, args.chunk),
+               "zururax": lambda size, depth: zururax_config(size, depth),
                "qwen2": lambda size, depth: qwen2_config(size, depth)}
     out = {"compare": " beside ".join(designs), "dtype": args.dtype, "batch": args.batch, "prompt_len": PROMPT_LEN,
            "prefill_tokens": PREFILL_TOKENS, "chunk": args.chunk, "sizes": {}}
@@ -544,7 +568,7 @@ def main() -> int:
                         help="with --impl reference: its attention backend (default: DISTIE_ATTN, else auto)")
     parser.add_argument("--ref-device", default=None, help=argparse.SUPPRESS)  # "cpu": a dry run of the reference arm
     parser.add_argument("--designs", default=None, help="with --compare: only these of its designs, with commas between them")
-    parser.add_argument("--compare", default=None, choices=["zelasun", "fovudra"],
+    parser.add_argument("--compare", default=None, choices=["zelasun", "fovudra", "zururax"],
                         help="time another design beside the Qwen2 decoder at equal layer sizes instead of the default run")
     parser.add_argument("--chunk", type=int, default=1024,
                         help="with --compare: the chunk (Zelasun) or window (Fovudra) of the design's attention")

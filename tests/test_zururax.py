@@ -717,7 +717,7 @@ def test_a_far_token_decides_through_the_whole_model(kit):
         got[far] = helpers.collect(steps, helpers.run_schedule(TraceSession(engine), steps))
         assert_close(got[far], {"a": expected[far]}, tolerance(kit), f"far token {far}")
     moved = row_errors(expected[7][-60:], expected[8][-60:])
-    assert float(moved.min()) > 20 * tolerance(kit), "the far token does not show in the late logits: the test's weights are too weak"
+    assert float(moved.min()) > 2 * tolerance(kit) and float(moved.median()) > 0.5, "the far token does not show in the late logits: the test's weights are too weak"
 
 
 def test_long_decoding_beside_requests_that_come_and_go(kit):
