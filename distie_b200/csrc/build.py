@@ -50,7 +50,7 @@ CUDA_UNITS: dict[str, list[str]] = {
     # models whose feed-forward routes tokens to experts (both dtypes)
     "routed": ["routed.cu"],
     # models whose attention reads one latent row per token; gated and squared-ReLU activations on float32 products
-    "latent": ["latent.cu"],
+    "latent": ["latent.cu", "latent_attention_mma.cu"],
 }
 _HEADERS = ["common.cuh", "tcgen05.cuh", "no_alloc.h"]
 

@@ -92,7 +92,7 @@ constexpr int kEpilogueStageBytes = 32 * 32 * 4;  // per epilogue warp
 template <int BN, int EPI>
 __device__ __forceinline__ void store_accumulator(uint32_t lane_base, int row0, int lane, int n0,
                                                   void* __restrict__ out, int ldo, int M, int N, int inter, int part,
-                                                  unsigned char* stage) {
+                                                  unsigned char* stage, float limit = 0.f) {
   const int rows_valid = M - row0;
   if (EPI == GEMM_EPI_SWIGLU) {
     constexpr int HALF = BN / 2;
@@ -105,7 +105,12 @@ __device__ __forceinline__ void store_accumulator(uint32_t lane_base, int row0, 
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
         const float g = __uint_as_float(gate[j]), u = __uint_as_float(up[j]);
-        v[j] = __fdividef(g * u, 1.f + __expf(-g));
+        if (limit > 0.f) {  // the capped form: min(g, limit) sigmoid(1.702 min(g, limit)) (clamp(u, +-limit) + 1)
+          const float gc = fminf(g, limit), uc = fminf(fmaxf(u, -limit), limit);
+          v[j] = gc * (uc + 1.f) / (1.f + expf(-1.702f * gc));
+        } else {
+          v[j] = __fdividef(g * u, 1.f + __expf(-g));
+        }
       }
       const int col = n0 + c0;
       if (lane < rows_valid && col < inter)
@@ -447,7 +452,7 @@ template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(kGemmWideThreads, 1)
 gemm_tcgen05_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                             void* __restrict__ out, int ldo, int N, int K, int inter, int num_tiles,
-                            const GroupedTiles tiles, int* __restrict__ error) {
+                            const GroupedTiles tiles, float limit, int* __restrict__ error) {
   extern __shared__ unsigned char raw[];
   auto& sm = *reinterpret_cast<GemmShared<BN, STAGES>*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
   constexpr uint32_t TMEM_COLS = 512;
@@ -548,7 +553,7 @@ gemm_tcgen05_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t lane_base = tmem + buffer * ACC_STRIDE + ((uint32_t)(quadrant * 32) << 16);
       // (rows of the box past the group's own are not stored: the output ends at row m0 + rows for this tile)
-      store_accumulator<BN, EPI>(lane_base, m0 + quadrant * 32, lane, n0, out, ldo, m0 + rows, N, inter, part, epilogue_stage);
+      store_accumulator<BN, EPI>(lane_base, m0 + quadrant * 32, lane, n0, out, ldo, m0 + rows, N, inter, part, epilogue_stage, limit);
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(&sm.accum_empty[buffer]);
@@ -1103,10 +1108,11 @@ extern "C" int distie_gemm_tcgen05(const void* x, int ldx, const void* w, void* 
 }
 
 // The grouped product (see gemm_tcgen05_grouped_kernel): a[rows_a, K] sorted by group, w[groups * w_rows, K]; the tile
-// list lives on the device.  epi 2: w_rows = 2 * inter and out[rows_a, inter] bfloat16 = silu(a Wg^T) * (a Wu^T);
+// list lives on the device.  epi 2: w_rows = 2 * inter and out[rows_a, inter] bfloat16 = silu(a Wg^T) * (a Wu^T), or with
+// limit > 0 its capped form g' sigmoid(1.702 g') (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit);
 // epi 1: w_rows = N and out[rows_a, N] float32.  K a multiple of 8, rows 16-byte aligned.
 extern "C" int distie_gemm_tcgen05_grouped(const void* a, int lda, int rows_a, const void* w, int groups, int w_rows,
-                                           void* out, int ldo, int N, int K, int epi, const int* num_m_tiles,
+                                           void* out, int ldo, int N, int K, int epi, float limit, const int* num_m_tiles,
                                            const int* tile_group, const int* tile_first, const int* tile_rows,
                                            int max_m_tiles, int sm_count, int* error, cudaStream_t stream) {
   if (rows_a <= 0 || max_m_tiles <= 0) return 0;
@@ -1132,7 +1138,7 @@ extern "C" int distie_gemm_tcgen05_grouped(const void* a, int lda, int rows_a, c
     const int num_tiles = max_m_tiles * ((N + 127) / 128);
     gemm_tcgen05_grouped_kernel<256, 4, GEMM_EPI_SWIGLU><<<num_tiles < sm_count ? num_tiles : sm_count, kGemmWideThreads,
                                                            shared, stream>>>(map_a, map_b, out, ldo, 2 * N, K, N, num_tiles,
-                                                                             tiles, error);
+                                                                             tiles, limit, error);
   } else if (epi == GEMM_EPI_F32) {
     if (w_rows != N) return DISTIE_ERR_ARG;
     if ((status = make_map(&map_b, w, groups * w_rows, K, K, 256)) != 0) return status;
@@ -1146,7 +1152,7 @@ extern "C" int distie_gemm_tcgen05_grouped(const void* a, int lda, int rows_a, c
     }
     const int num_tiles = max_m_tiles * ((N + 255) / 256);
     gemm_tcgen05_grouped_kernel<256, 4, GEMM_EPI_F32><<<num_tiles < sm_count ? num_tiles : sm_count, kGemmWideThreads, shared,
-                                                        stream>>>(map_a, map_b, out, ldo, N, K, 0, num_tiles, tiles, error);
+                                                        stream>>>(map_a, map_b, out, ldo, N, K, 0, num_tiles, tiles, 0.f, error);
   } else {
     return DISTIE_ERR_ARG;
   }

@@ -185,13 +185,13 @@ latent_attention_kernel(const T* __restrict__ folded, const T* __restrict__ rota
                         const int* __restrict__ positions, const int* __restrict__ token_seq,
                         const int* __restrict__ seq_seat, const int* __restrict__ block_table, int table_width,
                         const T* __restrict__ k_cache, int page_size, int num_pages, float scale,
-                        const float* __restrict__ sink, int splits, int* __restrict__ error) {
+                        const float* __restrict__ sink, int splits, int first, int* __restrict__ error) {
   extern __shared__ float latent_s[];
   constexpr int kRow = RMAX * 32;
   float* q_s = latent_s;                                   // [HB][kRow], zero beyond the row
   float* acc_s = q_s + HB * kRow;                          // [warps][HB][rank]
   float* ml_s = acc_s + (size_t)kLatentWarps * HB * rank;  // [warps][HB][2]
-  const int t = blockIdx.x, h0 = blockIdx.y * HB, split = blockIdx.z;
+  const int t = first + blockIdx.x, h0 = blockIdx.y * HB, split = blockIdx.z;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int row = rank + rot;
   const int live = min(HB, heads - h0);
@@ -307,8 +307,8 @@ latent_attention_kernel(const T* __restrict__ folded, const T* __restrict__ rota
 template <typename T>
 __global__ void __launch_bounds__(128)
 latent_merge_kernel(const float* __restrict__ partial, T* __restrict__ out, int tokens, int heads, int rank, int splits,
-                    const float* __restrict__ sink) {
-  const int t = blockIdx.x, head = blockIdx.y;
+                    const float* __restrict__ sink, int first) {
+  const int t = first + blockIdx.x, head = blockIdx.y;
   const size_t stride = (size_t)tokens * heads * (rank + 2);
   const float* mine = partial + ((size_t)t * heads + head) * (size_t)(rank + 2);
   float top = sink ? sink[head] : -INFINITY;
@@ -335,20 +335,20 @@ static int launch_latent_attention(const void* folded, const void* rotated, void
                                    int heads, int rank, int rot, const int* positions, const int* token_seq,
                                    const int* seq_seat, const int* block_table, int table_width, const void* k_cache,
                                    int page_size, int num_pages, float scale, const float* sink, int splits,
-                                   int* error, cudaStream_t stream) {
+                                   int first, int count, int* error, cudaStream_t stream) {
   const size_t shared = ((size_t)HB * RMAX * 32 + (size_t)kLatentWarps * HB * rank + kLatentWarps * HB * 2) * sizeof(float);
   auto kernel = latent_attention_kernel<T, RMAX, HB>;
   if (shared > 48 * 1024) {
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
     if (err != cudaSuccess) return (int)err;
   }
-  const dim3 grid(tokens, (heads + HB - 1) / HB, splits);
+  const dim3 grid(count, (heads + HB - 1) / HB, splits);
   kernel<<<grid, kLatentWarps * 32, shared, stream>>>((const T*)folded, (const T*)rotated, (T*)out, partial, tokens, heads,
                                                       rank, rot, positions, token_seq, seq_seat, block_table, table_width,
-                                                      (const T*)k_cache, page_size, num_pages, scale, sink, splits, error);
+                                                      (const T*)k_cache, page_size, num_pages, scale, sink, splits, first, error);
   DISTIE_LAUNCH_CHECK();
   if (splits > 1) {
-    latent_merge_kernel<T><<<dim3(tokens, heads), 128, 0, stream>>>(partial, (T*)out, tokens, heads, rank, splits, sink);
+    latent_merge_kernel<T><<<dim3(count, heads), 128, 0, stream>>>(partial, (T*)out, tokens, heads, rank, splits, sink, first);
     DISTIE_LAUNCH_CHECK();
   }
   return 0;
@@ -358,13 +358,13 @@ template <typename T>
 static int latent_attention_any(const void* folded, const void* rotated, void* out, float* partial, int tokens, int heads,
                                 int rank, int rot, const int* positions, const int* token_seq, const int* seq_seat,
                                 const int* block_table, int table_width, const void* k_cache, int page_size,
-                                int num_pages, float scale, const float* sink, int splits, int* error,
-                                cudaStream_t stream) {
+                                int num_pages, float scale, const float* sink, int splits, int first, int count,
+                                int* error, cudaStream_t stream) {
   const int row = rank + rot;
 #define DISTIE_LATENT(RMAX, HB)                                                                                     \
   return launch_latent_attention<T, RMAX, HB>(folded, rotated, out, partial, tokens, heads, rank, rot, positions,  \
                                               token_seq, seq_seat, block_table, table_width, k_cache, page_size,   \
-                                              num_pages, scale, sink, splits, error, stream)
+                                              num_pages, scale, sink, splits, first, count, error, stream)
   if (row <= 128) DISTIE_LATENT(4, 8);
   if (row <= 256) DISTIE_LATENT(8, 8);
   if (row <= 512) DISTIE_LATENT(16, 4);
@@ -437,8 +437,10 @@ extern "C" int distie_latent_attention(const void* folded, const void* rotated, 
                                        int heads, int rank, int rot, const int* positions, const int* token_seq,
                                        const int* seq_seat, const int* block_table, int table_width,
                                        const void* k_cache, int page_size, int num_pages, float scale,
-                                       const float* sink, int splits, int dtype, int* error, cudaStream_t stream) {
-  if (tokens <= 0) return 0;
+                                       const float* sink, int splits, int first, int count, int dtype, int* error,
+                                       cudaStream_t stream) {
+  if (tokens <= 0 || count <= 0) return 0;
+  if (first < 0 || first + count > tokens) return DISTIE_ERR_ARG;
   if (heads < 1 || rank < 1 || rot < 0 || page_size < 1 || table_width < 1 || splits < 1 || splits > 65535 ||
       (splits > 1 && !partial) || (heads + 1) / 2 > 65535)
     return DISTIE_ERR_ARG;
@@ -446,11 +448,11 @@ extern "C" int distie_latent_attention(const void* folded, const void* rotated, 
   if (dtype == DISTIE_BF16)
     return latent_attention_any<__nv_bfloat16>(folded, rotated, out, partial, tokens, heads, rank, rot, positions,
                                                token_seq, seq_seat, block_table, table_width, k_cache, page_size,
-                                               num_pages, scale, sink, splits, error, stream);
+                                               num_pages, scale, sink, splits, first, count, error, stream);
   if (dtype == DISTIE_F32)
     return latent_attention_any<float>(folded, rotated, out, partial, tokens, heads, rank, rot, positions, token_seq,
                                        seq_seat, block_table, table_width, k_cache, page_size, num_pages, scale, sink,
-                                       splits, error, stream);
+                                       splits, first, count, error, stream);
   return DISTIE_ERR_UNSUPPORTED;
 }
 

@@ -1,0 +1,339 @@
+// Attention through a latent for portions of prompts, on the tensor cores (bfloat16).
+//
+// Every token of the cache is ONE row [latent (rank) | rotated key part (rot)] that all heads share; a query of a
+// head is [its plain part folded into the latent's space (rank) | its rotated part (rot)].  The score of a query and
+// a key is the product of the two rows, and the value of a key is the first `rank` columns of its row, so one tile
+// of rows in shared memory serves both products.
+//
+// A portion is cut into tiles of 64 consecutive tokens of one request.  One CTA of 8 warps takes one tile and one
+// head and walks the keys the tile can see in blocks of 64 (cp.async, two stages; rows past the last visible key
+// are zero-filled; rows are located one by one through the block table, so any page size works):
+//
+//   S = Q K^T    warp (rg, kh), rg = 0..3, kh = 0..1: query rows 16 rg .. 16 rg + 15 against keys 32 kh .. 32 kh + 31
+//                of the block, reduction over the whole row; mma.sync.m16n8k16, float32 accumulators
+//   softmax      online, float32, base-2 exponentials; the two warps of a row group exchange their block maxima
+//                through shared memory, so both keep the same running maximum, and each keeps the sum of its own
+//                keys (the sums are added at the end)
+//   P            bfloat16 into shared memory, [64 rows x 64 keys]
+//   O += P V     warp (rg, ch): the same 16 rows, value columns ch VC/2 .. (ch + 1) VC/2 - 1, reduction over the
+//                block's 64 keys; O stays in registers (VC/4 floats a thread)
+//   end          O / (sum + exp(sink - max)): the sink of the head is a term of the denominator without a value
+//
+// Key j is visible to the row at position p iff j <= p.  It depends on positions only, so the result does not depend
+// on how the prompt was cut.  rank and rot multiples of 8 (16-byte copies), rank <= VC, rank + rot <= ROW; other
+// sizes are refused (-2) and the caller uses the size-agnostic kernel.
+#include "common.cuh"
+
+namespace distie {
+
+constexpr int kLmWarps = 8;
+constexpr int kLmRows = 64;
+constexpr int kLmKeys = 64;
+
+__device__ __forceinline__ uint32_t lm_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void lm_cp16(uint32_t dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes));
+}
+__device__ __forceinline__ void lm_commit() { asm volatile("cp.async.commit_group;"); }
+template <int N>
+__device__ __forceinline__ void lm_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
+__device__ __forceinline__ void lm_ldmatrix(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void lm_ldmatrix_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void lm_mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t lm_pack(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+// The two warps of row group `rg` meet (barrier 0 is __syncthreads).
+__device__ __forceinline__ void lm_pair_sync(int rg) { asm volatile("bar.sync %0, 64;" ::"r"(rg + 1) : "memory"); }
+
+// Byte offset of 16-byte chunk `chunk` of row `row` in a tile of CHUNKS chunks a row (CHUNKS a multiple of 8); the
+// chunk is XOR-ed with the row so that the eight rows of an ldmatrix hit different banks.
+template <int CHUNKS>
+__device__ __forceinline__ uint32_t lm_offset(int row, int chunk) {
+  return (uint32_t)((row * CHUNKS + (chunk ^ (row & 7))) * 16);
+}
+
+template <int ROW, int VC>
+__global__ void __launch_bounds__(kLmWarps * 32, 1)
+latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ folded, const __nv_bfloat16* __restrict__ rotated,
+                            __nv_bfloat16* __restrict__ out, int tokens, int heads, int rank, int rot,
+                            const int* __restrict__ q_tiles, const int* __restrict__ positions,
+                            const int* __restrict__ token_seq, const int* __restrict__ seq_seat,
+                            const int* __restrict__ block_table, int table_width,
+                            const __nv_bfloat16* __restrict__ k_cache, int page_size, int page_shift, int num_pages,
+                            float scale_log2, const float* __restrict__ sink, int* __restrict__ error) {
+  constexpr int CHUNKS = ROW / 8;
+  constexpr int TILE_BYTES = kLmKeys * ROW * 2;
+  constexpr int P_CHUNKS = kLmKeys / 8;
+  constexpr int NT = VC / 16;  // tiles of 8 value columns a warp owns
+  static_assert(ROW % 64 == 0 && VC % 32 == 0 && VC <= ROW, "tile sizes");
+  extern __shared__ __align__(128) unsigned char lm_s[];
+  unsigned char* q_s = lm_s;
+  unsigned char* k_s = q_s + TILE_BYTES;                       // two stages
+  unsigned char* p_s = k_s + 2 * TILE_BYTES;                   // [64][64] bfloat16
+  float* stat_s = reinterpret_cast<float*>(p_s + kLmRows * kLmKeys * 2);  // [2][64]
+
+  // Tiles late in a request see the most keys and take longest: start them first.  A tile of the list holds up to
+  // 2 * kLmRows rows: two CTAs take its halves.
+  const int slot = gridDim.y - 1 - blockIdx.y, head = blockIdx.x;
+  const int tile = slot >> 1, half = slot & 1;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int rg = warp & 3, kh = warp >> 2;
+  const int g = lane >> 2, c = lane & 3;
+  const int t0 = q_tiles[2 * tile] + half * kLmRows;
+  const int rows = min(kLmRows, q_tiles[2 * tile + 1] - half * kLmRows);
+  if (rows <= 0) return;
+  const int row_len = rank + rot;
+  const int p0 = positions[t0];
+  const int seat = seq_seat[token_seq[t0]];
+  const int* table = block_table + (size_t)seat * table_width;
+  const int p_last = p0 + rows - 1;
+  const int num_blocks = p_last / kLmKeys + 1;
+  const int live_chunks = row_len / 8;               // chunks of a row that hold data; the rest stay zero
+  const int ksteps = (row_len + 15) / 16;
+
+  auto load_q = [&]() {
+    for (int idx = threadIdx.x; idx < kLmRows * CHUNKS; idx += kLmWarps * 32) {
+      const int r = idx / CHUNKS, ch = idx % CHUNKS;
+      const int t = t0 + (r < rows ? r : 0);
+      const __nv_bfloat16* src = folded;
+      int bytes = 0;
+      if (r < rows && ch < live_chunks) {
+        bytes = 16;
+        src = ch * 8 < rank ? folded + ((size_t)head * tokens + t) * rank + ch * 8
+                            : rotated + ((size_t)t * heads + head) * rot + (ch * 8 - rank);
+      }
+      lm_cp16(lm_smem(q_s + lm_offset<CHUNKS>(r, ch)), src, bytes);
+    }
+  };
+  auto load_k = [&](int block, int stage) {
+    const int kb = block * kLmKeys;
+    for (int idx = threadIdx.x; idx < kLmKeys * CHUNKS; idx += kLmWarps * 32) {
+      const int r = idx / CHUNKS, ch = idx % CHUNKS;
+      const int key = kb + r;
+      const __nv_bfloat16* src = k_cache;
+      int bytes = 0;
+      if (key <= p_last && ch < live_chunks) {
+        const int column = page_shift >= 0 ? key >> page_shift : key / page_size;
+        const int within = page_shift >= 0 ? key & (page_size - 1) : key % page_size;
+        const int page = column < table_width ? table[column] : -1;
+        if (page < 0 || page >= num_pages) {
+          if (error) atomicExch(error, 3);
+        } else {
+          bytes = 16;
+          src = k_cache + ((size_t)page * page_size + within) * (size_t)row_len + ch * 8;
+        }
+      }
+      lm_cp16(lm_smem(k_s + stage * TILE_BYTES + lm_offset<CHUNKS>(r, ch)), src, bytes);
+    }
+  };
+
+  load_q();
+  load_k(0, 0);
+  lm_commit();
+
+  float o[NT][4];
+#pragma unroll
+  for (int i = 0; i < NT; ++i)
+#pragma unroll
+    for (int r = 0; r < 4; ++r) o[i][r] = 0.f;
+  float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.f, 0.f};
+  const int pos_row[2] = {p0 + rg * 16 + g, p0 + rg * 16 + g + 8};
+  const int a_row = rg * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;  // the row this lane names in an A-operand ldmatrix
+
+  for (int block = 0; block < num_blocks; ++block) {
+    const int stage = block & 1;
+    if (block + 1 < num_blocks) load_k(block + 1, stage ^ 1);
+    lm_commit();
+    lm_wait<1>();
+    __syncthreads();
+    const unsigned char* k_tile = k_s + stage * TILE_BYTES;
+
+    // ---- S = Q K^T: 16 rows x 32 keys a warp ------------------------------------------------------------------
+    float s[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int r = 0; r < 4; ++r) s[i][r] = 0.f;
+#pragma unroll 4
+    for (int ks = 0; ks < ksteps; ++ks) {
+      uint32_t a[4];
+      lm_ldmatrix(a, lm_smem(q_s + lm_offset<CHUNKS>(a_row, 2 * ks + (lane >> 4))));
+#pragma unroll
+      for (int np = 0; np < 2; ++np) {
+        uint32_t b[4];
+        const int key_row = kh * 32 + np * 16 + (lane & 7) + (lane >> 4) * 8;
+        lm_ldmatrix(b, lm_smem(k_tile + lm_offset<CHUNKS>(key_row, 2 * ks + ((lane >> 3) & 1))));
+        lm_mma(s[2 * np], a, b[0], b[1]);
+        lm_mma(s[2 * np + 1], a, b[2], b[3]);
+      }
+    }
+
+    // ---- mask and block maximum -------------------------------------------------------------------------------
+    const int kb = block * kLmKeys + kh * 32;
+    float tile_max[2] = {-INFINITY, -INFINITY};
+    if (kb + 31 <= p0 + rg * 16) {  // wholly visible to every row of the warp
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int r = 0; r < 4; ++r) tile_max[r >> 1] = fmaxf(tile_max[r >> 1], s[i][r]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          const int key = kb + i * 8 + 2 * c + (r & 1);
+          s[i][r] = key <= pos_row[r >> 1] ? s[i][r] : -INFINITY;
+          tile_max[r >> 1] = fmaxf(tile_max[r >> 1], s[i][r]);
+        }
+      }
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      float m = tile_max[h];
+      m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+      m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+      tile_max[h] = m;
+      if (c == 0) stat_s[kh * kLmRows + rg * 16 + g + 8 * h] = m;
+    }
+    lm_pair_sync(rg);
+    // row_max holds scale_log2 * (largest raw score so far); the scale is positive, so the order is the same.
+    float corr[2], shift[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const float m = fmaxf(tile_max[h], stat_s[(kh ^ 1) * kLmRows + rg * 16 + g + 8 * h]);
+      const float m_new = fmaxf(row_max[h], m * scale_log2);
+      corr[h] = (m_new == -INFINITY) ? 1.f : exp2f(row_max[h] - m_new);
+      row_max[h] = m_new;
+      row_sum[h] *= corr[h];
+      shift[h] = m_new == -INFINITY ? 0.f : -m_new;
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const float p = exp2f(fmaf(s[i][r], scale_log2, shift[r >> 1]));  // exp2(-inf) = 0 for hidden keys
+        s[i][r] = p;
+        row_sum[r >> 1] += p;
+      }
+      const int chunk = kh * 4 + i;
+      const int r0 = rg * 16 + g, r1 = r0 + 8;
+      *reinterpret_cast<uint32_t*>(p_s + lm_offset<P_CHUNKS>(r0, chunk) + 4 * c) = lm_pack(s[i][0], s[i][1]);
+      *reinterpret_cast<uint32_t*>(p_s + lm_offset<P_CHUNKS>(r1, chunk) + 4 * c) = lm_pack(s[i][2], s[i][3]);
+    }
+#pragma unroll
+    for (int i = 0; i < NT; ++i) {
+      o[i][0] *= corr[0]; o[i][1] *= corr[0];
+      o[i][2] *= corr[1]; o[i][3] *= corr[1];
+    }
+    lm_pair_sync(rg);
+
+    // ---- O += P V: 16 rows x VC/2 columns a warp ----------------------------------------------------------------
+#pragma unroll
+    for (int kk = 0; kk < kLmKeys / 16; ++kk) {
+      uint32_t a[4];
+      lm_ldmatrix(a, lm_smem(p_s + lm_offset<P_CHUNKS>(a_row, 2 * kk + (lane >> 4))));
+      const int key_row = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+#pragma unroll
+      for (int dp = 0; dp < NT / 2; ++dp) {
+        uint32_t b[4];
+        lm_ldmatrix_trans(b, lm_smem(k_tile + lm_offset<CHUNKS>(key_row, kh * NT + 2 * dp + (lane >> 4))));
+        lm_mma(o[2 * dp], a, b[0], b[1]);
+        lm_mma(o[2 * dp + 1], a, b[2], b[3]);
+      }
+    }
+    __syncthreads();  // this stage, P and the maxima are overwritten in the next iteration
+  }
+  lm_wait<0>();
+
+  // ---- the two warps of a row group add their sums; the sink joins the denominator; store -----------------------
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    float l = row_sum[h];
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    row_sum[h] = l;
+    if (c == 0) stat_s[kh * kLmRows + rg * 16 + g + 8 * h] = l;
+  }
+  lm_pair_sync(rg);
+  const float sink2 = sink ? sink[head] * 1.4426950408889634f : -INFINITY;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int row = rg * 16 + g + 8 * h;
+    const float l = row_sum[h] + stat_s[(kh ^ 1) * kLmRows + row];
+    const float top = fmaxf(row_max[h], sink2);
+    const float shrink = row_max[h] == -INFINITY ? 0.f : exp2f(row_max[h] - top);
+    const float den = l * shrink + (sink ? exp2f(sink2 - top) : 0.f);
+    const float inv = den > 0.f ? shrink / den : 0.f;
+    if (row < rows) {
+      __nv_bfloat16* dst = out + ((size_t)head * tokens + t0 + row) * rank;
+#pragma unroll
+      for (int i = 0; i < NT; ++i) {
+        const int col = (kh * NT + i) * 8 + 2 * c;
+        if (col < rank) *reinterpret_cast<uint32_t*>(dst + col) = lm_pack(o[i][2 * h] * inv, o[i][2 * h + 1] * inv);
+      }
+    }
+  }
+}
+
+template <int ROW, int VC>
+static int launch_latent_mma(const void* folded, const void* rotated, void* out, int tokens, int heads, int rank, int rot,
+                             const int* q_tiles, int num_tiles, const int* positions, const int* token_seq,
+                             const int* seq_seat, const int* block_table, int table_width, const void* k_cache,
+                             int page_size, int num_pages, float scale, const float* sink, int* error,
+                             cudaStream_t stream) {
+  const size_t shared = 3 * (size_t)kLmKeys * ROW * 2 + kLmRows * kLmKeys * 2 + 2 * kLmRows * sizeof(float);
+  auto kernel = latent_attention_mma_kernel<ROW, VC>;
+  cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+  if (err != cudaSuccess) return (int)err;
+  int page_shift = -1;
+  if ((page_size & (page_size - 1)) == 0)
+    for (page_shift = 0; (1 << page_shift) < page_size;) ++page_shift;
+  const dim3 grid(heads, 2 * num_tiles);
+  kernel<<<grid, kLmWarps * 32, shared, stream>>>(
+      (const __nv_bfloat16*)folded, (const __nv_bfloat16*)rotated, (__nv_bfloat16*)out, tokens, heads, rank, rot, q_tiles,
+      positions, token_seq, seq_seat, block_table, table_width, (const __nv_bfloat16*)k_cache, page_size, page_shift,
+      num_pages, scale * 1.4426950408889634f, sink, error);
+  DISTIE_LAUNCH_CHECK();
+  return 0;
+}
+
+}  // namespace distie
+
+using namespace distie;
+
+// Tokens per tile of `q_tiles` ([num_tiles, 2] int32: first token of the tile, number of rows <= 128).
+// folded [heads, tokens, rank], rotated [tokens, heads, rot], out [heads, tokens, rank]: bfloat16, contiguous.
+// -2: sizes this kernel does not take.
+extern "C" int distie_latent_attention_tiles(const void* folded, const void* rotated, void* out, int tokens, int heads,
+                                             int rank, int rot, const int* q_tiles, int num_tiles,
+                                             const int* positions, const int* token_seq, const int* seq_seat,
+                                             const int* block_table, int table_width, const void* k_cache,
+                                             int page_size, int num_pages, float scale, const float* sink, int* error,
+                                             cudaStream_t stream) {
+  if (num_tiles <= 0 || tokens <= 0) return 0;
+  if (heads < 1 || rank < 1 || rot < 0 || page_size < 1 || table_width < 1) return DISTIE_ERR_ARG;
+  if (rank % 8 || rot % 8 || !(scale > 0.f) || 2 * (long long)num_tiles > 65535) return -2;
+  const int row = rank + rot;
+#define DISTIE_LATENT_MMA(ROW, VC)                                                                                   \
+  return launch_latent_mma<ROW, VC>(folded, rotated, out, tokens, heads, rank, rot, q_tiles, num_tiles, positions,   \
+                                    token_seq, seq_seat, block_table, table_width, k_cache, page_size, num_pages,   \
+                                    scale, sink, error, stream)
+  if (row <= 128) DISTIE_LATENT_MMA(128, 128);
+  if (row <= 320 && rank <= 256) DISTIE_LATENT_MMA(320, 256);
+  if (row <= 576 && rank <= 512) DISTIE_LATENT_MMA(576, 512);
+#undef DISTIE_LATENT_MMA
+  return -2;
+}

@@ -744,8 +744,8 @@ class DeviceKernels(KernelSet):
         if code == 1 and (x.stride(0) % 8 or hidden % 8 or ff % 8):
             # rows that are no multiples of 16 bytes: the float32 form of the grouped products takes any size
             x, gate_up, down, code = x.float(), gate_up.float(), down.float(), 0
-        if code == 1 and self.dtype == torch.bfloat16 and tokens * top >= _GROUPED_TENSOR_CORE_PAIRS and limit is None:
-            return self._routed_swiglu_tcgen05(x, ids, weights, gate_up, down, scale_input)
+        if code == 1 and self.dtype == torch.bfloat16 and tokens * top >= _GROUPED_TENSOR_CORE_PAIRS:
+            return self._routed_swiglu_tcgen05(x, ids, weights, gate_up, down, scale_input, limit)
         tile = function("distie_routed_tile")(code, hidden, ff, tokens * top, experts)
         words = function("distie_route_plan_words")(tokens * top, experts, tile)
         plan = torch.empty(words, dtype=torch.int32, device=x.device)
@@ -762,7 +762,7 @@ class DeviceKernels(KernelSet):
         self._ran("routed_swiglu", 3)
         return out
 
-    def _routed_swiglu_tcgen05(self, x, ids, weights, gate_up, down, scale_input):
+    def _routed_swiglu_tcgen05(self, x, ids, weights, gate_up, down, scale_input, limit=None):
         """Prompt portions in bfloat16: the rows sorted by expert (and scaled by their weights) are gathered once, and
         both products run on the tcgen05 tile kernel over a list of row tiles that stays on the device."""
         tokens, top = ids.shape
@@ -781,11 +781,12 @@ class DeviceKernels(KernelSet):
                                                int(bool(scale_input)), 1, stream), "routed_gather")
         mid = torch.empty((pairs, ff), dtype=x.dtype, device=x.device)
         check(function("distie_gemm_tcgen05_grouped")(
-            gathered.data_ptr(), hidden, pairs, gate_up.data_ptr(), experts, 2 * ff, mid.data_ptr(), ff, ff, hidden, 2, base,
+            gathered.data_ptr(), hidden, pairs, gate_up.data_ptr(), experts, 2 * ff, mid.data_ptr(), ff, ff, hidden, 2,
+            float(limit) if limit is not None else 0.0, base,
             tile_expert, tile_first, tile_rows, max_tiles, self.sm_count, error, stream), "gemm_tcgen05_grouped")
         sorted_out = torch.empty((pairs, hidden), dtype=torch.float32, device=x.device)
         check(function("distie_gemm_tcgen05_grouped")(
-            mid.data_ptr(), ff, pairs, down.data_ptr(), experts, hidden, sorted_out.data_ptr(), hidden, hidden, ff, 1, base,
+            mid.data_ptr(), ff, pairs, down.data_ptr(), experts, hidden, sorted_out.data_ptr(), hidden, hidden, ff, 1, 0.0, base,
             tile_expert, tile_first, tile_rows, max_tiles, self.sm_count, error, stream), "gemm_tcgen05_grouped")
         out = torch.empty((top, tokens, hidden), dtype=torch.float32, device=x.device)
         check(function("distie_routed_scatter")(sorted_out.data_ptr(), base, pairs, experts, tile, out.data_ptr(), hidden,
@@ -867,8 +868,25 @@ class DeviceKernels(KernelSet):
         if kv.k.dtype != folded.dtype or not folded.is_contiguous() or not rotated.is_contiguous() or not out.is_contiguous():
             raise KernelError("latent_attention: contiguous queries and output of the cache's type are expected")
         tokens = step.num_tokens
+        sink_ptr = sink.data_ptr() if sink is not None else None
+        # Portions of prompts: tiles of consecutive tokens of a request on the tensor cores.  Single tokens (they
+        # come first in a step) and whatever the tiled kernel refuses go to the size-agnostic kernel.
+        first, count = 0, tokens
+        if self.dtype == torch.bfloat16 and step.num_q_tiles and tokens > step.num_decode_tokens:
+            code = function("distie_latent_attention_tiles")(
+                folded.data_ptr(), rotated.data_ptr(), out.data_ptr(), tokens, num_heads, kv_rank, rot_dim,
+                step.q_tiles.data_ptr(), step.num_q_tiles, step.positions.data_ptr(), step.token_seq.data_ptr(),
+                step.seq_seat.data_ptr(), kv.block_table.data_ptr(), kv.block_table.shape[-1], kv.k.data_ptr(),
+                kv.page_size, kv.num_pages, float(scale), sink_ptr, self.error_flag.data_ptr(), self._stream(),
+            )
+            if code != -2:
+                check(code, "latent_attention_tiles")
+                self._ran("latent_attention_mma")
+                count = step.num_decode_tokens
+        if count <= 0:
+            return
         # Steps of few tokens over long requests: the keys are split so that the machine is filled.
-        blocks = tokens * -(-num_heads // 4)
+        blocks = count * -(-num_heads // 4)
         splits = max(1, min(-(-2 * self.sm_count // max(blocks, 1)), -(-max(int(step.max_kv_len), 1) // 128), 64))
         partial = None
         if splits > 1:
@@ -879,7 +897,7 @@ class DeviceKernels(KernelSet):
                 folded.data_ptr(), rotated.data_ptr(), out.data_ptr(), partial.data_ptr() if partial is not None else None,
                 tokens, num_heads, kv_rank, rot_dim, step.positions.data_ptr(), step.token_seq.data_ptr(),
                 step.seq_seat.data_ptr(), kv.block_table.data_ptr(), kv.block_table.shape[-1], kv.k.data_ptr(),
-                kv.page_size, kv.num_pages, float(scale), sink.data_ptr() if sink is not None else None, splits,
+                kv.page_size, kv.num_pages, float(scale), sink_ptr, splits, first, count,
                 _CODE[folded.dtype], self.error_flag.data_ptr(), self._stream(),
             ),
             "latent_attention",

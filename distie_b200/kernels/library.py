@@ -67,14 +67,15 @@ _SIGNATURES: dict[str, tuple[str, list]] = {
     "distie_route_plan": ("routed", [P, P, I, I, I, I, P, P, P]),
     "distie_routed_gather": ("routed", [P, I, P, I, I, I, P, I, I, I, P]),
     "distie_routed_scatter": ("routed", [P, P, I, I, I, P, I, I, P]),
-    "distie_gemm_tcgen05_grouped": ("bf16", [P, I, I, P, I, I, P, I, I, I, I, P, P, P, P, I, I, P, P]),
+    "distie_gemm_tcgen05_grouped": ("bf16", [P, I, I, P, I, I, P, I, I, I, I, F, P, P, P, P, I, I, P, P]),
     "distie_routed_swiglu": ("routed", [P, I, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P, P]),
     "distie_latent_kv_write": (
         "latent", [P, I, I, L, I, P, I, P, I, F, P, I, P, P, P, P, I, P, F, I, I, P, I, I, I, I, I, P, P]
     ),
     "distie_latent_q_prepare": ("latent", [P, I, I, L, I, I, I, I, P, P, F, I, I, P, P, I, P]),
     "distie_latent_attention_scratch_floats": ("latent", [I, I, I, I]),
-    "distie_latent_attention": ("latent", [P, P, P, P, I, I, I, I, P, P, P, P, I, P, I, I, F, P, I, I, P, P]),
+    "distie_latent_attention": ("latent", [P, P, P, P, I, I, I, I, P, P, P, P, I, P, I, I, F, P, I, I, I, I, P, P]),
+    "distie_latent_attention_tiles": ("latent", [P, P, P, I, I, I, I, P, I, P, P, P, P, I, P, I, I, F, P, P, P]),
     "distie_latent_gate": ("latent", [P, I, I, I, P, I, I, L, P, I, I, P]),
     "distie_glu_act": ("latent", [P, I, I, L, I, I, I, F, P, I, I, L, P, I, I, P]),
     "distie_gated_rmsnorm": ("state", [P, I, P, I, I, L, P, I, P, I, I, I, I, F, I, I, P]),
