@@ -220,34 +220,47 @@ latent_attention_kernel(const T* __restrict__ folded, const T* __restrict__ rota
 #pragma unroll
     for (int i = 0; i < RMAX; ++i) acc[hb][i] = 0.f;
   }
-  for (int key = begin + warp; key < end; key += kLatentWarps) {
+  // A key's row is on its way while the one before it is used: the loop is a chain of dependent steps (the running
+  // maximum), and a load issued inside it would be waited for in full at every key.
+  auto fetch = [&](int key, float (&dst)[RMAX]) -> bool {
     const int column = key / page_size;
     const int page = column < table_width ? table[column] : -1;
     if (page < 0 || page >= num_pages) {
       if (lane == 0 && error) atomicExch(error, 3);
-      continue;
+      return false;
     }
     const T* src = k_cache + ((size_t)page * page_size + key % page_size) * (size_t)row;
-    float kr[RMAX];
 #pragma unroll
     for (int i = 0; i < RMAX; ++i) {
       const int e = lane + 32 * i;
-      kr[i] = e < row ? to_float(src[e]) : 0.f;
+      dst[i] = e < row ? to_float(src[e]) : 0.f;
     }
+    return true;
+  };
+  float kr[RMAX];
+  bool have = begin + warp < end && fetch(begin + warp, kr);
+  for (int key = begin + warp; key < end; key += kLatentWarps) {
+    float ahead[RMAX];
+    const bool have_ahead = key + kLatentWarps < end && fetch(key + kLatentWarps, ahead);
+    if (have) {
 #pragma unroll
-    for (int hb = 0; hb < HB; ++hb) {
-      float dot = 0.f;
+      for (int hb = 0; hb < HB; ++hb) {
+        float dot = 0.f;
 #pragma unroll
-      for (int i = 0; i < RMAX; ++i) dot += q_s[hb * kRow + lane + 32 * i] * kr[i];
-      const float s = warp_sum(dot) * scale;
-      const float m_new = fmaxf(m[hb], s);
-      const float corr = expf(m[hb] - m_new);
-      const float p = expf(s - m_new);
-      l[hb] = l[hb] * corr + p;
+        for (int i = 0; i < RMAX; ++i) dot += q_s[hb * kRow + lane + 32 * i] * kr[i];
+        const float s = warp_sum(dot) * scale;
+        const float m_new = fmaxf(m[hb], s);
+        const float corr = expf(m[hb] - m_new);
+        const float p = expf(s - m_new);
+        l[hb] = l[hb] * corr + p;
 #pragma unroll
-      for (int i = 0; i < RMAX; ++i) acc[hb][i] = acc[hb][i] * corr + p * kr[i];
-      m[hb] = m_new;
+        for (int i = 0; i < RMAX; ++i) acc[hb][i] = acc[hb][i] * corr + p * kr[i];
+        m[hb] = m_new;
+      }
     }
+    have = have_ahead;
+#pragma unroll
+    for (int i = 0; i < RMAX; ++i) kr[i] = ahead[i];
   }
 #pragma unroll
   for (int hb = 0; hb < HB; ++hb) {
@@ -309,6 +322,7 @@ __global__ void __launch_bounds__(128)
 latent_merge_kernel(const float* __restrict__ partial, T* __restrict__ out, int tokens, int heads, int rank, int splits,
                     const float* __restrict__ sink, int first) {
   const int t = first + blockIdx.x, head = blockIdx.y;
+  __shared__ float weight_s[64];  // the launcher takes at most 64 splits
   const size_t stride = (size_t)tokens * heads * (rank + 2);
   const float* mine = partial + ((size_t)t * heads + head) * (size_t)(rank + 2);
   float top = sink ? sink[head] : -INFINITY;
@@ -319,14 +333,17 @@ latent_merge_kernel(const float* __restrict__ partial, T* __restrict__ out, int 
     if (ms != -INFINITY) den += mine[s * stride + rank + 1] * expf(ms - top);
   }
   const float inv = den > 0.f ? 1.f / den : 0.f;
+  for (int s = threadIdx.x; s < splits; s += blockDim.x) {
+    const float ms = mine[s * stride + rank];
+    weight_s[s] = ms != -INFINITY ? expf(ms - top) * inv : 0.f;  // (a split without keys wrote zeros)
+  }
+  __syncthreads();
   T* dst = out + ((size_t)head * tokens + t) * rank;
   for (int e = threadIdx.x; e < rank; e += blockDim.x) {
     float total = 0.f;
-    for (int s = 0; s < splits; ++s) {
-      const float ms = mine[s * stride + rank];
-      if (ms != -INFINITY) total += mine[s * stride + e] * expf(ms - top);
-    }
-    dst[e] = from_float<T>(total * inv);
+#pragma unroll 8
+    for (int s = 0; s < splits; ++s) total += mine[s * stride + e] * weight_s[s];
+    dst[e] = from_float<T>(total);
   }
 }
 
@@ -441,7 +458,7 @@ extern "C" int distie_latent_attention(const void* folded, const void* rotated, 
                                        cudaStream_t stream) {
   if (tokens <= 0 || count <= 0) return 0;
   if (first < 0 || first + count > tokens) return DISTIE_ERR_ARG;
-  if (heads < 1 || rank < 1 || rot < 0 || page_size < 1 || table_width < 1 || splits < 1 || splits > 65535 ||
+  if (heads < 1 || rank < 1 || rot < 0 || page_size < 1 || table_width < 1 || splits < 1 || splits > 64 ||
       (splits > 1 && !partial) || (heads + 1) / 2 > 65535)
     return DISTIE_ERR_ARG;
   if (rank + rot > 1024) return DISTIE_ERR_UNSUPPORTED;

@@ -5,18 +5,19 @@
 // a key is the product of the two rows, and the value of a key is the first `rank` columns of its row, so one tile
 // of rows in shared memory serves both products.
 //
-// A portion is cut into tiles of 64 consecutive tokens of one request.  One CTA of 8 warps takes one tile and one
+// A portion is cut into tiles of 64 consecutive tokens of one request.  One CTA of 16 warps takes one tile and one
 // head and walks the keys the tile can see in blocks of 64 (cp.async, two stages; rows past the last visible key
 // are zero-filled; rows are located one by one through the block table, so any page size works):
 //
-//   S = Q K^T    warp (rg, kh), rg = 0..3, kh = 0..1: query rows 16 rg .. 16 rg + 15 against keys 32 kh .. 32 kh + 31
-//                of the block, reduction over the whole row; mma.sync.m16n8k16, float32 accumulators
-//   softmax      online, float32, base-2 exponentials; the two warps of a row group exchange their block maxima
-//                through shared memory, so both keep the same running maximum, and each keeps the sum of its own
+//   S = Q K^T    warp (rg, kh), rg = 0..3, kh = 0..3: query rows 16 rg .. 16 rg + 15 against keys 16 kh .. 16 kh + 15
+//                of the block, reduction over the whole row (even and odd steps of it into accumulators of their
+//                own, so that twice as many products are in flight); mma.sync.m16n8k16, float32 accumulators
+//   softmax      online, float32, base-2 exponentials; the four warps of a row group exchange their block maxima
+//                through shared memory, so all keep the same running maximum, and each keeps the sum of its own
 //                keys (the sums are added at the end)
 //   P            bfloat16 into shared memory, [64 rows x 64 keys]
-//   O += P V     warp (rg, ch): the same 16 rows, value columns ch VC/2 .. (ch + 1) VC/2 - 1, reduction over the
-//                block's 64 keys; O stays in registers (VC/4 floats a thread)
+//   O += P V     warp (rg, ch): the same 16 rows, value columns ch VC/4 .. (ch + 1) VC/4 - 1, reduction over the
+//                block's 64 keys; O stays in registers (VC/8 floats a thread)
 //   end          O / (sum + exp(sink - max)): the sink of the head is a term of the denominator without a value
 //
 // Key j is visible to the row at position p iff j <= p.  It depends on positions only, so the result does not depend
@@ -26,7 +27,8 @@
 
 namespace distie {
 
-constexpr int kLmWarps = 8;
+constexpr int kLmParts = 4;              // warps of a row group: parts of a block's keys, and of the value columns
+constexpr int kLmWarps = 4 * kLmParts;
 constexpr int kLmRows = 64;
 constexpr int kLmKeys = 64;
 
@@ -55,8 +57,10 @@ __device__ __forceinline__ uint32_t lm_pack(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
-// The two warps of row group `rg` meet (barrier 0 is __syncthreads).
-__device__ __forceinline__ void lm_pair_sync(int rg) { asm volatile("bar.sync %0, 64;" ::"r"(rg + 1) : "memory"); }
+// The warps of row group `rg` meet (barrier 0 is __syncthreads).
+__device__ __forceinline__ void lm_group_sync(int rg) {
+  asm volatile("bar.sync %0, %1;" ::"r"(rg + 1), "n"(kLmParts * 32) : "memory");
+}
 
 // Byte offset of 16-byte chunk `chunk` of row `row` in a tile of CHUNKS chunks a row (CHUNKS a multiple of 8); the
 // chunk is XOR-ed with the row so that the eight rows of an ldmatrix hit different banks.
@@ -77,20 +81,20 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ folded, const __nv
   constexpr int CHUNKS = ROW / 8;
   constexpr int TILE_BYTES = kLmKeys * ROW * 2;
   constexpr int P_CHUNKS = kLmKeys / 8;
-  constexpr int NT = VC / 16;  // tiles of 8 value columns a warp owns
-  static_assert(ROW % 64 == 0 && VC % 32 == 0 && VC <= ROW, "tile sizes");
+  constexpr int NT = VC / (8 * kLmParts);  // tiles of 8 value columns a warp owns
+  static_assert(ROW % 64 == 0 && NT % 2 == 0 && VC <= ROW, "tile sizes");
   extern __shared__ __align__(128) unsigned char lm_s[];
   unsigned char* q_s = lm_s;
   unsigned char* k_s = q_s + TILE_BYTES;                       // two stages
   unsigned char* p_s = k_s + 2 * TILE_BYTES;                   // [64][64] bfloat16
-  float* stat_s = reinterpret_cast<float*>(p_s + kLmRows * kLmKeys * 2);  // [2][64]
+  float* stat_s = reinterpret_cast<float*>(p_s + kLmRows * kLmKeys * 2);  // [parts][64]
 
   // Tiles late in a request see the most keys and take longest: start them first.  A tile of the list holds up to
   // 2 * kLmRows rows: two CTAs take its halves.
   const int slot = gridDim.y - 1 - blockIdx.y, head = blockIdx.x;
   const int tile = slot >> 1, half = slot & 1;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int rg = warp & 3, kh = warp >> 2;
+  const int rg = warp & 3, kh = warp >> 2;  // row group; part of the keys and of the columns
   const int g = lane >> 2, c = lane & 3;
   const int t0 = q_tiles[2 * tile] + half * kLmRows;
   const int rows = min(kLmRows, q_tiles[2 * tile + 1] - half * kLmRows);
@@ -161,37 +165,49 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ folded, const __nv
     __syncthreads();
     const unsigned char* k_tile = k_s + stage * TILE_BYTES;
 
-    // ---- S = Q K^T: 16 rows x 32 keys a warp ------------------------------------------------------------------
-    float s[4][4];
+    // ---- S = Q K^T: 16 rows x 16 keys a warp ------------------------------------------------------------------
+    float s[2][4], s_odd[2][4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < 2; ++i)
 #pragma unroll
-      for (int r = 0; r < 4; ++r) s[i][r] = 0.f;
-#pragma unroll 4
-    for (int ks = 0; ks < ksteps; ++ks) {
-      uint32_t a[4];
-      lm_ldmatrix(a, lm_smem(q_s + lm_offset<CHUNKS>(a_row, 2 * ks + (lane >> 4))));
-#pragma unroll
-      for (int np = 0; np < 2; ++np) {
-        uint32_t b[4];
-        const int key_row = kh * 32 + np * 16 + (lane & 7) + (lane >> 4) * 8;
-        lm_ldmatrix(b, lm_smem(k_tile + lm_offset<CHUNKS>(key_row, 2 * ks + ((lane >> 3) & 1))));
-        lm_mma(s[2 * np], a, b[0], b[1]);
-        lm_mma(s[2 * np + 1], a, b[2], b[3]);
-      }
+      for (int r = 0; r < 4; ++r) s[i][r] = s_odd[i][r] = 0.f;
+    const int key_row = kh * 16 + (lane & 7) + (lane >> 4) * 8;
+#pragma unroll 2
+    for (int ks = 0; ks + 1 < ksteps; ks += 2) {
+      uint32_t a0[4], b0[4], a1[4], b1[4];
+      lm_ldmatrix(a0, lm_smem(q_s + lm_offset<CHUNKS>(a_row, 2 * ks + (lane >> 4))));
+      lm_ldmatrix(b0, lm_smem(k_tile + lm_offset<CHUNKS>(key_row, 2 * ks + ((lane >> 3) & 1))));
+      lm_ldmatrix(a1, lm_smem(q_s + lm_offset<CHUNKS>(a_row, 2 * ks + 2 + (lane >> 4))));
+      lm_ldmatrix(b1, lm_smem(k_tile + lm_offset<CHUNKS>(key_row, 2 * ks + 2 + ((lane >> 3) & 1))));
+      lm_mma(s[0], a0, b0[0], b0[1]);
+      lm_mma(s[1], a0, b0[2], b0[3]);
+      lm_mma(s_odd[0], a1, b1[0], b1[1]);
+      lm_mma(s_odd[1], a1, b1[2], b1[3]);
     }
+    if (ksteps & 1) {
+      const int ks = ksteps - 1;
+      uint32_t a0[4], b0[4];
+      lm_ldmatrix(a0, lm_smem(q_s + lm_offset<CHUNKS>(a_row, 2 * ks + (lane >> 4))));
+      lm_ldmatrix(b0, lm_smem(k_tile + lm_offset<CHUNKS>(key_row, 2 * ks + ((lane >> 3) & 1))));
+      lm_mma(s[0], a0, b0[0], b0[1]);
+      lm_mma(s[1], a0, b0[2], b0[3]);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int r = 0; r < 4; ++r) s[i][r] += s_odd[i][r];
 
     // ---- mask and block maximum -------------------------------------------------------------------------------
-    const int kb = block * kLmKeys + kh * 32;
+    const int kb = block * kLmKeys + kh * 16;
     float tile_max[2] = {-INFINITY, -INFINITY};
-    if (kb + 31 <= p0 + rg * 16) {  // wholly visible to every row of the warp
+    if (kb + 15 <= p0 + rg * 16) {  // wholly visible to every row of the warp
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
+      for (int i = 0; i < 2; ++i)
 #pragma unroll
         for (int r = 0; r < 4; ++r) tile_max[r >> 1] = fmaxf(tile_max[r >> 1], s[i][r]);
     } else {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
+      for (int i = 0; i < 2; ++i) {
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
           const int key = kb + i * 8 + 2 * c + (r & 1);
@@ -208,12 +224,14 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ folded, const __nv
       tile_max[h] = m;
       if (c == 0) stat_s[kh * kLmRows + rg * 16 + g + 8 * h] = m;
     }
-    lm_pair_sync(rg);
+    lm_group_sync(rg);
     // row_max holds scale_log2 * (largest raw score so far); the scale is positive, so the order is the same.
     float corr[2], shift[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-      const float m = fmaxf(tile_max[h], stat_s[(kh ^ 1) * kLmRows + rg * 16 + g + 8 * h]);
+      float m = tile_max[h];
+#pragma unroll
+      for (int part = 0; part < kLmParts; ++part) m = fmaxf(m, stat_s[part * kLmRows + rg * 16 + g + 8 * h]);
       const float m_new = fmaxf(row_max[h], m * scale_log2);
       corr[h] = (m_new == -INFINITY) ? 1.f : exp2f(row_max[h] - m_new);
       row_max[h] = m_new;
@@ -221,14 +239,14 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ folded, const __nv
       shift[h] = m_new == -INFINITY ? 0.f : -m_new;
     }
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < 2; ++i) {
 #pragma unroll
       for (int r = 0; r < 4; ++r) {
         const float p = exp2f(fmaf(s[i][r], scale_log2, shift[r >> 1]));  // exp2(-inf) = 0 for hidden keys
         s[i][r] = p;
         row_sum[r >> 1] += p;
       }
-      const int chunk = kh * 4 + i;
+      const int chunk = kh * 2 + i;
       const int r0 = rg * 16 + g, r1 = r0 + 8;
       *reinterpret_cast<uint32_t*>(p_s + lm_offset<P_CHUNKS>(r0, chunk) + 4 * c) = lm_pack(s[i][0], s[i][1]);
       *reinterpret_cast<uint32_t*>(p_s + lm_offset<P_CHUNKS>(r1, chunk) + 4 * c) = lm_pack(s[i][2], s[i][3]);
@@ -238,18 +256,18 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ folded, const __nv
       o[i][0] *= corr[0]; o[i][1] *= corr[0];
       o[i][2] *= corr[1]; o[i][3] *= corr[1];
     }
-    lm_pair_sync(rg);
+    lm_group_sync(rg);
 
-    // ---- O += P V: 16 rows x VC/2 columns a warp ----------------------------------------------------------------
+    // ---- O += P V: 16 rows x VC/4 columns a warp ----------------------------------------------------------------
 #pragma unroll
     for (int kk = 0; kk < kLmKeys / 16; ++kk) {
       uint32_t a[4];
       lm_ldmatrix(a, lm_smem(p_s + lm_offset<P_CHUNKS>(a_row, 2 * kk + (lane >> 4))));
-      const int key_row = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+      const int value_row = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
 #pragma unroll
       for (int dp = 0; dp < NT / 2; ++dp) {
         uint32_t b[4];
-        lm_ldmatrix_trans(b, lm_smem(k_tile + lm_offset<CHUNKS>(key_row, kh * NT + 2 * dp + (lane >> 4))));
+        lm_ldmatrix_trans(b, lm_smem(k_tile + lm_offset<CHUNKS>(value_row, kh * NT + 2 * dp + (lane >> 4))));
         lm_mma(o[2 * dp], a, b[0], b[1]);
         lm_mma(o[2 * dp + 1], a, b[2], b[3]);
       }
@@ -258,7 +276,7 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ folded, const __nv
   }
   lm_wait<0>();
 
-  // ---- the two warps of a row group add their sums; the sink joins the denominator; store -----------------------
+  // ---- the warps of a row group add their sums; the sink joins the denominator; store -----------------------
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     float l = row_sum[h];
@@ -267,12 +285,14 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ folded, const __nv
     row_sum[h] = l;
     if (c == 0) stat_s[kh * kLmRows + rg * 16 + g + 8 * h] = l;
   }
-  lm_pair_sync(rg);
+  lm_group_sync(rg);
   const float sink2 = sink ? sink[head] * 1.4426950408889634f : -INFINITY;
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int row = rg * 16 + g + 8 * h;
-    const float l = row_sum[h] + stat_s[(kh ^ 1) * kLmRows + row];
+    float l = 0.f;
+#pragma unroll
+    for (int part = 0; part < kLmParts; ++part) l += stat_s[part * kLmRows + row];
     const float top = fmaxf(row_max[h], sink2);
     const float shrink = row_max[h] == -INFINITY ? 0.f : exp2f(row_max[h] - top);
     const float den = l * shrink + (sink ? exp2f(sink2 - top) : 0.f);
@@ -294,7 +314,7 @@ static int launch_latent_mma(const void* folded, const void* rotated, void* out,
                              const int* seq_seat, const int* block_table, int table_width, const void* k_cache,
                              int page_size, int num_pages, float scale, const float* sink, int* error,
                              cudaStream_t stream) {
-  const size_t shared = 3 * (size_t)kLmKeys * ROW * 2 + kLmRows * kLmKeys * 2 + 2 * kLmRows * sizeof(float);
+  const size_t shared = 3 * (size_t)kLmKeys * ROW * 2 + kLmRows * kLmKeys * 2 + kLmParts * kLmRows * sizeof(float);
   auto kernel = latent_attention_mma_kernel<ROW, VC>;
   cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
   if (err != cudaSuccess) return (int)err;

@@ -885,9 +885,10 @@ class DeviceKernels(KernelSet):
                 count = step.num_decode_tokens
         if count <= 0:
             return
-        # Steps of few tokens over long requests: the keys are split so that the machine is filled.
+        # Steps of few tokens over long requests: the keys are split so that the machine is filled (four blocks of
+        # four warps an SM; a warp walks its keys one after the other, so short walks are what hides their latency).
         blocks = count * -(-num_heads // 4)
-        splits = max(1, min(-(-2 * self.sm_count // max(blocks, 1)), -(-max(int(step.max_kv_len), 1) // 128), 64))
+        splits = max(1, min(-(-4 * self.sm_count // max(blocks, 1)), -(-max(int(step.max_kv_len), 1) // 64), 64))
         partial = None
         if splits > 1:
             floats = function("distie_latent_attention_scratch_floats")(tokens, num_heads, kv_rank, splits)
