@@ -473,6 +473,26 @@ extern "C" int distie_latent_attention(const void* folded, const void* rotated, 
   return DISTIE_ERR_UNSUPPORTED;
 }
 
+// The splits' partial results [splits, tokens, heads, rank + 2] of tokens first .. first + count - 1 into out
+// [heads, tokens, rank]; the head's sink joins the denominator here.
+extern "C" int distie_latent_merge(const float* partial, void* out, int tokens, int heads, int rank, int splits,
+                                   const float* sink, int first, int count, int dtype, cudaStream_t stream) {
+  if (count <= 0) return 0;
+  if (!partial || tokens < 1 || heads < 1 || heads > 65535 || rank < 1 || splits < 1 || splits > 64 || first < 0 ||
+      first + count > tokens)
+    return DISTIE_ERR_ARG;
+  if (dtype == DISTIE_BF16)
+    latent_merge_kernel<__nv_bfloat16><<<dim3(count, heads), 128, 0, stream>>>(partial, (__nv_bfloat16*)out, tokens, heads,
+                                                                              rank, splits, sink, first);
+  else if (dtype == DISTIE_F32)
+    latent_merge_kernel<float><<<dim3(count, heads), 128, 0, stream>>>(partial, (float*)out, tokens, heads, rank, splits,
+                                                                       sink, first);
+  else
+    return DISTIE_ERR_UNSUPPORTED;
+  DISTIE_LAUNCH_CHECK();
+  return 0;
+}
+
 extern "C" int distie_latent_gate(const void* y, int tokens, int heads, int vdim, const float* gate, int gate_stride,
                                   int gate_slices, long long gate_slice_stride, void* out, int out_stride, int dtype,
                                   cudaStream_t stream) {

@@ -20,6 +20,12 @@
 //                block's 64 keys; O stays in registers (VC/8 floats a thread)
 //   end          O / (sum + exp(sink - max)): the sink of the head is a term of the denominator without a value
 //
+// Single tokens (SINGLE) run the same loop with the roles of the rows changed: the rows of a tile are the heads of
+// ONE token (16 RG of them a CTA), which all see the same keys, and the keys are cut into `splits` ranges of whole
+// blocks, a CTA each, so that a step of few tokens fills the machine.  With more than one split a CTA leaves, per
+// (token, head), the unnormalised sum, its maximum (natural-log units) and its sum of weights, in the layout that
+// the size-agnostic kernel's merge reads; the sink joins in the merge.
+//
 // Key j is visible to the row at position p iff j <= p.  It depends on positions only, so the result does not depend
 // on how the prompt was cut.  rank and rot multiples of 8 (16-byte copies), rank <= VC, rank + rot <= ROW; other
 // sizes are refused (-2) and the caller uses the size-agnostic kernel.
@@ -28,8 +34,6 @@
 namespace distie {
 
 constexpr int kLmParts = 4;              // warps of a row group: parts of a block's keys, and of the value columns
-constexpr int kLmWarps = 4 * kLmParts;
-constexpr int kLmRows = 64;
 constexpr int kLmKeys = 64;
 
 __device__ __forceinline__ uint32_t lm_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -69,15 +73,18 @@ __device__ __forceinline__ uint32_t lm_offset(int row, int chunk) {
   return (uint32_t)((row * CHUNKS + (chunk ^ (row & 7))) * 16);
 }
 
-template <int ROW, int VC>
-__global__ void __launch_bounds__(kLmWarps * 32, 1)
+template <int ROW, int VC, int RG, bool SINGLE>
+__global__ void __launch_bounds__(RG * kLmParts * 32, 1)
 latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ folded, const __nv_bfloat16* __restrict__ rotated,
                             __nv_bfloat16* __restrict__ out, int tokens, int heads, int rank, int rot,
                             const int* __restrict__ q_tiles, const int* __restrict__ positions,
                             const int* __restrict__ token_seq, const int* __restrict__ seq_seat,
                             const int* __restrict__ block_table, int table_width,
                             const __nv_bfloat16* __restrict__ k_cache, int page_size, int page_shift, int num_pages,
-                            float scale_log2, const float* __restrict__ sink, int* __restrict__ error) {
+                            float scale_log2, const float* __restrict__ sink, float* __restrict__ partial,
+                            int first, int* __restrict__ error) {
+  constexpr int kLmRows = 16 * RG;            // rows of a tile: tokens of a portion, or heads of a single token
+  constexpr int kLmThreads = RG * kLmParts * 32;
   constexpr int CHUNKS = ROW / 8;
   constexpr int TILE_BYTES = kLmKeys * ROW * 2;
   constexpr int P_CHUNKS = kLmKeys / 8;
@@ -85,33 +92,48 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ folded, const __nv
   static_assert(ROW % 64 == 0 && NT % 2 == 0 && VC <= ROW, "tile sizes");
   extern __shared__ __align__(128) unsigned char lm_s[];
   unsigned char* q_s = lm_s;
-  unsigned char* k_s = q_s + TILE_BYTES;                       // two stages
+  unsigned char* k_s = q_s + kLmRows * ROW * 2;                // two stages
   unsigned char* p_s = k_s + 2 * TILE_BYTES;                   // [64][64] bfloat16
   float* stat_s = reinterpret_cast<float*>(p_s + kLmRows * kLmKeys * 2);  // [parts][64]
 
-  // Tiles late in a request see the most keys and take longest: start them first.  A tile of the list holds up to
-  // 2 * kLmRows rows: two CTAs take its halves.
-  const int slot = gridDim.y - 1 - blockIdx.y, head = blockIdx.x;
-  const int tile = slot >> 1, half = slot & 1;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int rg = warp & 3, kh = warp >> 2;  // row group; part of the keys and of the columns
+  const int rg = warp % RG, kh = warp / RG;  // row group; part of the keys and of the columns
   const int g = lane >> 2, c = lane & 3;
-  const int t0 = q_tiles[2 * tile] + half * kLmRows;
-  const int rows = min(kLmRows, q_tiles[2 * tile + 1] - half * kLmRows);
+  // A portion's tile: `rows` consecutive tokens from t0, one head.  A single token: `rows` heads from h0, token t0.
+  // Tiles late in a request see the most keys and take longest: start them first.  A tile of the list holds up to
+  // 128 rows: two CTAs take its halves.
+  int t0, rows, h0;
+  if (SINGLE) {
+    t0 = first + blockIdx.y;
+    h0 = blockIdx.x * kLmRows;
+    rows = min(kLmRows, heads - h0);
+  } else {
+    const int slot = gridDim.y - 1 - blockIdx.y;
+    const int tile = slot >> 1, half = slot & 1;
+    h0 = blockIdx.x;
+    t0 = q_tiles[2 * tile] + half * kLmRows;
+    rows = min(kLmRows, q_tiles[2 * tile + 1] - half * kLmRows);
+  }
   if (rows <= 0) return;
   const int row_len = rank + rot;
   const int p0 = positions[t0];
   const int seat = seq_seat[token_seq[t0]];
   const int* table = block_table + (size_t)seat * table_width;
-  const int p_last = p0 + rows - 1;
-  const int num_blocks = p_last / kLmKeys + 1;
+  const int p_last = SINGLE ? p0 : p0 + rows - 1;
+  int block_begin = 0, block_end = p_last / kLmKeys + 1;
+  if (SINGLE && gridDim.z > 1) {
+    const int per = (block_end + gridDim.z - 1) / gridDim.z;
+    block_begin = min(block_end, (int)blockIdx.z * per);
+    block_end = min(block_end, block_begin + per);
+  }
   const int live_chunks = row_len / 8;               // chunks of a row that hold data; the rest stay zero
   const int ksteps = (row_len + 15) / 16;
 
   auto load_q = [&]() {
-    for (int idx = threadIdx.x; idx < kLmRows * CHUNKS; idx += kLmWarps * 32) {
+    for (int idx = threadIdx.x; idx < kLmRows * CHUNKS; idx += kLmThreads) {
       const int r = idx / CHUNKS, ch = idx % CHUNKS;
-      const int t = t0 + (r < rows ? r : 0);
+      const int live = r < rows ? r : 0;
+      const int t = SINGLE ? t0 : t0 + live, head = SINGLE ? h0 + live : h0;
       const __nv_bfloat16* src = folded;
       int bytes = 0;
       if (r < rows && ch < live_chunks) {
@@ -124,7 +146,7 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ folded, const __nv
   };
   auto load_k = [&](int block, int stage) {
     const int kb = block * kLmKeys;
-    for (int idx = threadIdx.x; idx < kLmKeys * CHUNKS; idx += kLmWarps * 32) {
+    for (int idx = threadIdx.x; idx < kLmKeys * CHUNKS; idx += kLmThreads) {
       const int r = idx / CHUNKS, ch = idx % CHUNKS;
       const int key = kb + r;
       const __nv_bfloat16* src = k_cache;
@@ -145,7 +167,7 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ folded, const __nv
   };
 
   load_q();
-  load_k(0, 0);
+  if (block_begin < block_end) load_k(block_begin, 0);
   lm_commit();
 
   float o[NT][4];
@@ -154,12 +176,12 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ folded, const __nv
 #pragma unroll
     for (int r = 0; r < 4; ++r) o[i][r] = 0.f;
   float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.f, 0.f};
-  const int pos_row[2] = {p0 + rg * 16 + g, p0 + rg * 16 + g + 8};
+  const int pos_row[2] = {SINGLE ? p0 : p0 + rg * 16 + g, SINGLE ? p0 : p0 + rg * 16 + g + 8};
   const int a_row = rg * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;  // the row this lane names in an A-operand ldmatrix
 
-  for (int block = 0; block < num_blocks; ++block) {
-    const int stage = block & 1;
-    if (block + 1 < num_blocks) load_k(block + 1, stage ^ 1);
+  for (int block = block_begin; block < block_end; ++block) {
+    const int stage = (block - block_begin) & 1;
+    if (block + 1 < block_end) load_k(block + 1, stage ^ 1);
     lm_commit();
     lm_wait<1>();
     __syncthreads();
@@ -200,7 +222,7 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ folded, const __nv
     // ---- mask and block maximum -------------------------------------------------------------------------------
     const int kb = block * kLmKeys + kh * 16;
     float tile_max[2] = {-INFINITY, -INFINITY};
-    if (kb + 15 <= p0 + rg * 16) {  // wholly visible to every row of the warp
+    if (kb + 15 <= (SINGLE ? p0 : p0 + rg * 16)) {  // wholly visible to every row of the warp
 #pragma unroll
       for (int i = 0; i < 2; ++i)
 #pragma unroll
@@ -286,46 +308,63 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ folded, const __nv
     if (c == 0) stat_s[kh * kLmRows + rg * 16 + g + 8 * h] = l;
   }
   lm_group_sync(rg);
-  const float sink2 = sink ? sink[head] * 1.4426950408889634f : -INFINITY;
+  const bool leave_parts = SINGLE && gridDim.z > 1;
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int row = rg * 16 + g + 8 * h;
     float l = 0.f;
 #pragma unroll
     for (int part = 0; part < kLmParts; ++part) l += stat_s[part * kLmRows + row];
+    if (row >= rows) continue;
+    const int t = SINGLE ? t0 : t0 + row, head = SINGLE ? h0 + row : h0;
+    if (leave_parts) {
+      // (a split without keys leaves zeros, a maximum of -inf and a sum of 0: the merge gives it no weight)
+      float* dst = partial + (((size_t)blockIdx.z * tokens + t) * heads + head) * (size_t)(rank + 2);
+#pragma unroll
+      for (int i = 0; i < NT; ++i) {
+        const int col = (kh * NT + i) * 8 + 2 * c;
+        if (col < rank) *reinterpret_cast<float2*>(dst + col) = make_float2(o[i][2 * h], o[i][2 * h + 1]);
+      }
+      if (kh == 0 && c == 0) {
+        dst[rank] = row_max[h] * 0.6931471805599453f;
+        dst[rank + 1] = l;
+      }
+      continue;
+    }
+    const float sink2 = sink ? sink[head] * 1.4426950408889634f : -INFINITY;
     const float top = fmaxf(row_max[h], sink2);
     const float shrink = row_max[h] == -INFINITY ? 0.f : exp2f(row_max[h] - top);
     const float den = l * shrink + (sink ? exp2f(sink2 - top) : 0.f);
     const float inv = den > 0.f ? shrink / den : 0.f;
-    if (row < rows) {
-      __nv_bfloat16* dst = out + ((size_t)head * tokens + t0 + row) * rank;
+    __nv_bfloat16* dst = out + ((size_t)head * tokens + t) * rank;
 #pragma unroll
-      for (int i = 0; i < NT; ++i) {
-        const int col = (kh * NT + i) * 8 + 2 * c;
-        if (col < rank) *reinterpret_cast<uint32_t*>(dst + col) = lm_pack(o[i][2 * h] * inv, o[i][2 * h + 1] * inv);
-      }
+    for (int i = 0; i < NT; ++i) {
+      const int col = (kh * NT + i) * 8 + 2 * c;
+      if (col < rank) *reinterpret_cast<uint32_t*>(dst + col) = lm_pack(o[i][2 * h] * inv, o[i][2 * h + 1] * inv);
     }
   }
 }
 
-template <int ROW, int VC>
+template <int ROW, int VC, int RG, bool SINGLE>
 static int launch_latent_mma(const void* folded, const void* rotated, void* out, int tokens, int heads, int rank, int rot,
                              const int* q_tiles, int num_tiles, const int* positions, const int* token_seq,
                              const int* seq_seat, const int* block_table, int table_width, const void* k_cache,
-                             int page_size, int num_pages, float scale, const float* sink, int* error,
-                             cudaStream_t stream) {
-  const size_t shared = 3 * (size_t)kLmKeys * ROW * 2 + kLmRows * kLmKeys * 2 + kLmParts * kLmRows * sizeof(float);
-  auto kernel = latent_attention_mma_kernel<ROW, VC>;
+                             int page_size, int num_pages, float scale, const float* sink, float* partial, int first,
+                             int count, int splits, int* error, cudaStream_t stream) {
+  constexpr int kRows = 16 * RG;
+  const size_t shared = (size_t)kRows * ROW * 2 + 2 * (size_t)kLmKeys * ROW * 2 + kRows * kLmKeys * 2 +
+                        kLmParts * kRows * sizeof(float);
+  auto kernel = latent_attention_mma_kernel<ROW, VC, RG, SINGLE>;
   cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
   if (err != cudaSuccess) return (int)err;
   int page_shift = -1;
   if ((page_size & (page_size - 1)) == 0)
     for (page_shift = 0; (1 << page_shift) < page_size;) ++page_shift;
-  const dim3 grid(heads, 2 * num_tiles);
-  kernel<<<grid, kLmWarps * 32, shared, stream>>>(
+  const dim3 grid = SINGLE ? dim3((heads + kRows - 1) / kRows, count, splits) : dim3(heads, 2 * num_tiles);
+  kernel<<<grid, RG * kLmParts * 32, shared, stream>>>(
       (const __nv_bfloat16*)folded, (const __nv_bfloat16*)rotated, (__nv_bfloat16*)out, tokens, heads, rank, rot, q_tiles,
       positions, token_seq, seq_seat, block_table, table_width, (const __nv_bfloat16*)k_cache, page_size, page_shift,
-      num_pages, scale * 1.4426950408889634f, sink, error);
+      num_pages, scale * 1.4426950408889634f, sink, partial, first, error);
   DISTIE_LAUNCH_CHECK();
   return 0;
 }
@@ -348,12 +387,45 @@ extern "C" int distie_latent_attention_tiles(const void* folded, const void* rot
   if (rank % 8 || rot % 8 || !(scale > 0.f) || 2 * (long long)num_tiles > 65535) return -2;
   const int row = rank + rot;
 #define DISTIE_LATENT_MMA(ROW, VC)                                                                                   \
-  return launch_latent_mma<ROW, VC>(folded, rotated, out, tokens, heads, rank, rot, q_tiles, num_tiles, positions,   \
-                                    token_seq, seq_seat, block_table, table_width, k_cache, page_size, num_pages,   \
-                                    scale, sink, error, stream)
+  return launch_latent_mma<ROW, VC, 4, false>(folded, rotated, out, tokens, heads, rank, rot, q_tiles, num_tiles,    \
+                                              positions, token_seq, seq_seat, block_table, table_width, k_cache,    \
+                                              page_size, num_pages, scale, sink, nullptr, 0, 0, 1, error, stream)
   if (row <= 128) DISTIE_LATENT_MMA(128, 128);
   if (row <= 320 && rank <= 256) DISTIE_LATENT_MMA(320, 256);
   if (row <= 576 && rank <= 512) DISTIE_LATENT_MMA(576, 512);
 #undef DISTIE_LATENT_MMA
+  return -2;
+}
+
+// Tokens first .. first + count - 1 of the step, each a single token of its request: their heads are the rows of a
+// tile.  `splits` ranges of key blocks (at most 64); with more than one, `partial` holds
+// [splits, tokens, heads, rank + 2] floats and the caller merges them (distie_latent_merge).  -2: sizes not taken.
+extern "C" int distie_latent_attention_single(const void* folded, const void* rotated, void* out, float* partial,
+                                              int tokens, int heads, int rank, int rot, const int* positions,
+                                              const int* token_seq, const int* seq_seat, const int* block_table,
+                                              int table_width, const void* k_cache, int page_size, int num_pages,
+                                              float scale, const float* sink, int splits, int first, int count,
+                                              int* error, cudaStream_t stream) {
+  if (count <= 0 || tokens <= 0) return 0;
+  if (heads < 1 || rank < 1 || rot < 0 || page_size < 1 || table_width < 1 || first < 0 || first + count > tokens ||
+      splits < 1 || splits > 64 || (splits > 1 && !partial))
+    return DISTIE_ERR_ARG;
+  if (rank % 8 || rot % 8 || !(scale > 0.f) || count > 65535) return -2;
+  const int row = rank + rot;
+#define DISTIE_LATENT_ONE(ROW, VC, RG)                                                                               \
+  return launch_latent_mma<ROW, VC, RG, true>(folded, rotated, out, tokens, heads, rank, rot, nullptr, 0, positions, \
+                                              token_seq, seq_seat, block_table, table_width, k_cache, page_size,    \
+                                              num_pages, scale, sink, partial, first, count, splits, error, stream)
+#define DISTIE_LATENT_SINGLE(ROW, VC)          \
+  do {                                         \
+    if (heads <= 16) DISTIE_LATENT_ONE(ROW, VC, 1); \
+    if (heads <= 32) DISTIE_LATENT_ONE(ROW, VC, 2); \
+    DISTIE_LATENT_ONE(ROW, VC, 4);             \
+  } while (0)
+  if (row <= 128) DISTIE_LATENT_SINGLE(128, 128);
+  if (row <= 320 && rank <= 256) DISTIE_LATENT_SINGLE(320, 256);
+  if (row <= 576 && rank <= 512) DISTIE_LATENT_SINGLE(576, 512);
+#undef DISTIE_LATENT_SINGLE
+#undef DISTIE_LATENT_ONE
   return -2;
 }

@@ -885,21 +885,43 @@ class DeviceKernels(KernelSet):
                 count = step.num_decode_tokens
         if count <= 0:
             return
-        # Steps of few tokens over long requests: the keys are split so that the machine is filled (four blocks of
-        # four warps an SM; a warp walks its keys one after the other, so short walks are what hides their latency).
-        blocks = count * -(-num_heads // 4)
-        splits = max(1, min(-(-4 * self.sm_count // max(blocks, 1)), -(-max(int(step.max_kv_len), 1) // 64), 64))
-        partial = None
-        if splits > 1:
+        common = (tokens, num_heads, kv_rank, rot_dim, step.positions.data_ptr(), step.token_seq.data_ptr(),
+                  step.seq_seat.data_ptr(), kv.block_table.data_ptr(), kv.block_table.shape[-1], kv.k.data_ptr(),
+                  kv.page_size, kv.num_pages, float(scale), sink_ptr)
+
+        def scratch(splits: int):
+            if splits <= 1:
+                return None
             floats = function("distie_latent_attention_scratch_floats")(tokens, num_heads, kv_rank, splits)
-            partial = torch.empty(floats, dtype=torch.float32, device=folded.device)
+            return torch.empty(floats, dtype=torch.float32, device=folded.device)
+
+        key_blocks = -(-max(int(step.max_kv_len), 1) // 64)
+        if self.dtype == torch.bfloat16:
+            # Single tokens on the tensor cores: a token's heads are the rows of a tile, and ranges of whole key
+            # blocks go to CTAs of their own until the machine is filled.
+            ctas = count * -(-num_heads // 64)
+            splits = max(1, min(-(-self.sm_count // ctas), key_blocks, 64))
+            partial = scratch(splits)
+            code = function("distie_latent_attention_single")(
+                folded.data_ptr(), rotated.data_ptr(), out.data_ptr(), partial.data_ptr() if partial is not None else None,
+                *common, splits, first, count, self.error_flag.data_ptr(), self._stream(),
+            )
+            if code != -2:
+                check(code, "latent_attention_single")
+                if splits > 1:
+                    check(function("distie_latent_merge")(partial.data_ptr(), out.data_ptr(), tokens, num_heads, kv_rank,
+                                                          splits, sink_ptr, first, count, self.code, self._stream()),
+                          "latent_merge")
+                self._ran("latent_attention_mma", 2 if splits > 1 else 1)
+                return
+        # Steps of few tokens over long requests: the keys are split so that the machine is filled.
+        blocks = count * -(-num_heads // 4)
+        splits = max(1, min(-(-2 * self.sm_count // max(blocks, 1)), -(-key_blocks // 2), 64))
+        partial = scratch(splits)
         check(
             function("distie_latent_attention")(
                 folded.data_ptr(), rotated.data_ptr(), out.data_ptr(), partial.data_ptr() if partial is not None else None,
-                tokens, num_heads, kv_rank, rot_dim, step.positions.data_ptr(), step.token_seq.data_ptr(),
-                step.seq_seat.data_ptr(), kv.block_table.data_ptr(), kv.block_table.shape[-1], kv.k.data_ptr(),
-                kv.page_size, kv.num_pages, float(scale), sink_ptr, splits, first, count,
-                _CODE[folded.dtype], self.error_flag.data_ptr(), self._stream(),
+                *common, splits, first, count, _CODE[folded.dtype], self.error_flag.data_ptr(), self._stream(),
             ),
             "latent_attention",
         )

@@ -75,6 +75,8 @@ _SIGNATURES: dict[str, tuple[str, list]] = {
     "distie_latent_q_prepare": ("latent", [P, I, I, L, I, I, I, I, P, P, F, I, I, P, P, I, P]),
     "distie_latent_attention_scratch_floats": ("latent", [I, I, I, I]),
     "distie_latent_attention": ("latent", [P, P, P, P, I, I, I, I, P, P, P, P, I, P, I, I, F, P, I, I, I, I, P, P]),
+    "distie_latent_attention_single": ("latent", [P, P, P, P, I, I, I, I, P, P, P, P, I, P, I, I, F, P, I, I, I, P, P]),
+    "distie_latent_merge": ("latent", [P, P, I, I, I, I, P, I, I, I, P]),
     "distie_latent_attention_tiles": ("latent", [P, P, P, I, I, I, I, P, I, P, P, P, P, I, P, I, I, F, P, P, P]),
     "distie_latent_gate": ("latent", [P, I, I, I, P, I, I, L, P, I, I, P]),
     "distie_glu_act": ("latent", [P, I, I, L, I, I, I, F, P, I, I, L, P, I, I, P]),
