@@ -322,21 +322,23 @@ __global__ void __launch_bounds__(128)
 latent_merge_kernel(const float* __restrict__ partial, T* __restrict__ out, int tokens, int heads, int rank, int splits,
                     const float* __restrict__ sink, int first) {
   const int t = first + blockIdx.x, head = blockIdx.y;
-  __shared__ float weight_s[64];  // the launcher takes at most 64 splits
+  __shared__ float weight_s[64], max_s[64], sum_s[64];  // the launchers take at most 64 splits
   const size_t stride = (size_t)tokens * heads * (rank + 2);
   const float* mine = partial + ((size_t)t * heads + head) * (size_t)(rank + 2);
-  float top = sink ? sink[head] : -INFINITY;
-  for (int s = 0; s < splits; ++s) top = fmaxf(top, mine[s * stride + rank]);
-  float den = sink ? expf(sink[head] - top) : 0.f;
-  for (int s = 0; s < splits; ++s) {
-    const float ms = mine[s * stride + rank];
-    if (ms != -INFINITY) den += mine[s * stride + rank + 1] * expf(ms - top);
-  }
-  const float inv = den > 0.f ? 1.f / den : 0.f;
+  // One round trip for all the splits' maxima and sums, a thread each; the rest of the bookkeeping is on chip.
   for (int s = threadIdx.x; s < splits; s += blockDim.x) {
-    const float ms = mine[s * stride + rank];
-    weight_s[s] = ms != -INFINITY ? expf(ms - top) * inv : 0.f;  // (a split without keys wrote zeros)
+    max_s[s] = mine[s * stride + rank];
+    sum_s[s] = mine[s * stride + rank + 1];
   }
+  __syncthreads();
+  float top = sink ? sink[head] : -INFINITY;
+  for (int s = 0; s < splits; ++s) top = fmaxf(top, max_s[s]);
+  float den = sink ? expf(sink[head] - top) : 0.f;
+  for (int s = 0; s < splits; ++s)
+    if (max_s[s] != -INFINITY) den += sum_s[s] * expf(max_s[s] - top);
+  const float inv = den > 0.f ? 1.f / den : 0.f;
+  for (int s = threadIdx.x; s < splits; s += blockDim.x)
+    weight_s[s] = max_s[s] != -INFINITY ? expf(max_s[s] - top) * inv : 0.f;  // (a split without keys wrote zeros)
   __syncthreads();
   T* dst = out + ((size_t)head * tokens + t) * rank;
   for (int e = threadIdx.x; e < rank; e += blockDim.x) {

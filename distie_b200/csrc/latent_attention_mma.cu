@@ -144,25 +144,30 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ folded, const __nv
       lm_cp16(lm_smem(q_s + lm_offset<CHUNKS>(r, ch)), src, bytes);
     }
   };
+  // A warp copies whole rows: the row's page is looked up once, and the lanes take its 16-byte pieces in turn.
   auto load_k = [&](int block, int stage) {
     const int kb = block * kLmKeys;
-    for (int idx = threadIdx.x; idx < kLmKeys * CHUNKS; idx += kLmThreads) {
-      const int r = idx / CHUNKS, ch = idx % CHUNKS;
+    for (int r = warp; r < kLmKeys; r += kLmThreads / 32) {
       const int key = kb + r;
       const __nv_bfloat16* src = k_cache;
-      int bytes = 0;
-      if (key <= p_last && ch < live_chunks) {
+      bool ok = key <= p_last;
+      if (ok) {
         const int column = page_shift >= 0 ? key >> page_shift : key / page_size;
         const int within = page_shift >= 0 ? key & (page_size - 1) : key % page_size;
         const int page = column < table_width ? table[column] : -1;
         if (page < 0 || page >= num_pages) {
-          if (error) atomicExch(error, 3);
+          if (lane == 0 && error) atomicExch(error, 3);
+          ok = false;
         } else {
-          bytes = 16;
-          src = k_cache + ((size_t)page * page_size + within) * (size_t)row_len + ch * 8;
+          src = k_cache + ((size_t)page * page_size + within) * (size_t)row_len;
         }
       }
-      lm_cp16(lm_smem(k_s + stage * TILE_BYTES + lm_offset<CHUNKS>(r, ch)), src, bytes);
+      const uint32_t dst = lm_smem(k_s + stage * TILE_BYTES) + r * (CHUNKS * 16);
+#pragma unroll
+      for (int ch = lane; ch < CHUNKS; ch += 32) {
+        const bool live = ok && ch < live_chunks;
+        lm_cp16(dst + ((ch ^ (r & 7)) * 16), live ? src + ch * 8 : k_cache, live ? 16 : 0);
+      }
     }
   };
 
@@ -178,6 +183,14 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ folded, const __nv
   float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.f, 0.f};
   const int pos_row[2] = {SINGLE ? p0 : p0 + rg * 16 + g, SINGLE ? p0 : p0 + rg * 16 + g + 8};
   const int a_row = rg * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;  // the row this lane names in an A-operand ldmatrix
+  const int key_row = kh * 16 + (lane & 7) + (lane >> 4) * 8;       // and in a B-operand ldmatrix of the scores
+  const uint32_t q_base = lm_smem(q_s) + a_row * (CHUNKS * 16);
+  uint32_t off_a[4], off_b[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    off_a[j] = ((2 * j + (lane >> 4)) ^ (a_row & 7)) * 16;
+    off_b[j] = ((2 * j + ((lane >> 3) & 1)) ^ (key_row & 7)) * 16;
+  }
 
   for (int block = block_begin; block < block_end; ++block) {
     const int stage = (block - block_begin) & 1;
@@ -193,26 +206,39 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ folded, const __nv
     for (int i = 0; i < 2; ++i)
 #pragma unroll
       for (int r = 0; r < 4; ++r) s[i][r] = s_odd[i][r] = 0.f;
-    const int key_row = kh * 16 + (lane & 7) + (lane >> 4) * 8;
-#pragma unroll 2
-    for (int ks = 0; ks + 1 < ksteps; ks += 2) {
-      uint32_t a0[4], b0[4], a1[4], b1[4];
-      lm_ldmatrix(a0, lm_smem(q_s + lm_offset<CHUNKS>(a_row, 2 * ks + (lane >> 4))));
-      lm_ldmatrix(b0, lm_smem(k_tile + lm_offset<CHUNKS>(key_row, 2 * ks + ((lane >> 3) & 1))));
-      lm_ldmatrix(a1, lm_smem(q_s + lm_offset<CHUNKS>(a_row, 2 * ks + 2 + (lane >> 4))));
-      lm_ldmatrix(b1, lm_smem(k_tile + lm_offset<CHUNKS>(key_row, 2 * ks + 2 + ((lane >> 3) & 1))));
-      lm_mma(s[0], a0, b0[0], b0[1]);
-      lm_mma(s[1], a0, b0[2], b0[3]);
-      lm_mma(s_odd[0], a1, b1[0], b1[1]);
-      lm_mma(s_odd[1], a1, b1[2], b1[3]);
+    // Four steps of the reduction span 128 bytes of a row; within them the piece a lane reads is the step's piece
+    // XOR-ed with its row, which is the same for every four steps: the offsets are made once.
+    const uint32_t k_base = lm_smem(k_tile) + key_row * (CHUNKS * 16);
+    const int quads = ksteps >> 2;
+    for (int quad = 0; quad < quads; ++quad) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t a[4], b[4];
+        lm_ldmatrix(a, q_base + quad * 128 + off_a[j]);
+        lm_ldmatrix(b, k_base + quad * 128 + off_b[j]);
+        if (j & 1) {
+          lm_mma(s_odd[0], a, b[0], b[1]);
+          lm_mma(s_odd[1], a, b[2], b[3]);
+        } else {
+          lm_mma(s[0], a, b[0], b[1]);
+          lm_mma(s[1], a, b[2], b[3]);
+        }
+      }
     }
-    if (ksteps & 1) {
-      const int ks = ksteps - 1;
-      uint32_t a0[4], b0[4];
-      lm_ldmatrix(a0, lm_smem(q_s + lm_offset<CHUNKS>(a_row, 2 * ks + (lane >> 4))));
-      lm_ldmatrix(b0, lm_smem(k_tile + lm_offset<CHUNKS>(key_row, 2 * ks + ((lane >> 3) & 1))));
-      lm_mma(s[0], a0, b0[0], b0[1]);
-      lm_mma(s[1], a0, b0[2], b0[3]);
+#pragma unroll
+    for (int j = 0; j < 3; ++j) {
+      if (4 * quads + j < ksteps) {
+        uint32_t a[4], b[4];
+        lm_ldmatrix(a, q_base + quads * 128 + off_a[j]);
+        lm_ldmatrix(b, k_base + quads * 128 + off_b[j]);
+        if (j & 1) {
+          lm_mma(s_odd[0], a, b[0], b[1]);
+          lm_mma(s_odd[1], a, b[2], b[3]);
+        } else {
+          lm_mma(s[0], a, b[0], b[1]);
+          lm_mma(s[1], a, b[2], b[3]);
+        }
+      }
     }
 #pragma unroll
     for (int i = 0; i < 2; ++i)
