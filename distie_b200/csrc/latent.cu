@@ -340,10 +340,12 @@ latent_merge_kernel(const float* __restrict__ partial, T* __restrict__ out, int 
   for (int s = threadIdx.x; s < splits; s += blockDim.x)
     weight_s[s] = max_s[s] != -INFINITY ? expf(max_s[s] - top) * inv : 0.f;  // (a split without keys wrote zeros)
   __syncthreads();
+  // A thread takes one column (the grid's z covers the row): its loads from the splits do not depend on one another.
   T* dst = out + ((size_t)head * tokens + t) * rank;
-  for (int e = threadIdx.x; e < rank; e += blockDim.x) {
+  const int e = blockIdx.z * blockDim.x + threadIdx.x;
+  if (e < rank) {
     float total = 0.f;
-#pragma unroll 8
+#pragma unroll 16
     for (int s = 0; s < splits; ++s) total += mine[s * stride + e] * weight_s[s];
     dst[e] = from_float<T>(total);
   }
@@ -367,7 +369,7 @@ static int launch_latent_attention(const void* folded, const void* rotated, void
                                                       (const T*)k_cache, page_size, num_pages, scale, sink, splits, first, error);
   DISTIE_LAUNCH_CHECK();
   if (splits > 1) {
-    latent_merge_kernel<T><<<dim3(count, heads), 128, 0, stream>>>(partial, (T*)out, tokens, heads, rank, splits, sink, first);
+    latent_merge_kernel<T><<<dim3(count, heads, (rank + 127) / 128), 128, 0, stream>>>(partial, (T*)out, tokens, heads, rank, splits, sink, first);
     DISTIE_LAUNCH_CHECK();
   }
   return 0;
@@ -484,10 +486,10 @@ extern "C" int distie_latent_merge(const float* partial, void* out, int tokens, 
       first + count > tokens)
     return DISTIE_ERR_ARG;
   if (dtype == DISTIE_BF16)
-    latent_merge_kernel<__nv_bfloat16><<<dim3(count, heads), 128, 0, stream>>>(partial, (__nv_bfloat16*)out, tokens, heads,
+    latent_merge_kernel<__nv_bfloat16><<<dim3(count, heads, (rank + 127) / 128), 128, 0, stream>>>(partial, (__nv_bfloat16*)out, tokens, heads,
                                                                               rank, splits, sink, first);
   else if (dtype == DISTIE_F32)
-    latent_merge_kernel<float><<<dim3(count, heads), 128, 0, stream>>>(partial, (float*)out, tokens, heads, rank, splits,
+    latent_merge_kernel<float><<<dim3(count, heads, (rank + 127) / 128), 128, 0, stream>>>(partial, (float*)out, tokens, heads, rank, splits,
                                                                        sink, first);
   else
     return DISTIE_ERR_UNSUPPORTED;
