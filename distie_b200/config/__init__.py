@@ -6,6 +6,7 @@ from .qwen2_config import ConfigError, Qwen2Config
 from .fovudra_config import FovudraConfig
 from .zelasun_config import ZelasunConfig
 from .zururax_config import ZururaxConfig
+from .zuzunex_config import ZuzunexConfig
 from .registry import (
     Architecture,
     architecture_of,
@@ -28,6 +29,7 @@ __all__ = [
     "Qwen2Config",
     "ZelasunConfig",
     "ZururaxConfig",
+    "ZuzunexConfig",
     "architecture_of",
     "get_architecture",
     "known_architectures",

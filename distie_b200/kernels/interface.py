@@ -200,12 +200,26 @@ class KernelSet(ABC):
     @abstractmethod
     def attention(self, qkv, out, step: StepTensors, kv: KvSlot, num_heads: int, num_kv_heads: int,
                   head_dim: int, window: int | None, scale: float, chunk: int | None = None,
-                  keep_first: int = 0) -> None:
+                  keep_first: int = 0, softcap: float = 0.0, sink=None) -> None:
         """Causal attention of every token over its request's pages, optionally only over the last
         ``window`` keys or over the keys of the token's own ``chunk``.  With a window, ``keep_first`` keeps
         the request's first that-many positions visible to every later token, at their true positions.
         The size of a value is the last dimension of ``kv.v`` and may differ from ``head_dim``; ``out`` is
-        ``[T, heads * value size]``."""
+        ``[T, heads * value size]``.  ``softcap > 0``: a score ``s = q . k * scale`` becomes ``softcap * tanh(s /
+        softcap)``.  ``sink [heads]`` (float32): the softmax's denominator also holds ``exp(sink_h)``, a term with
+        no key and no value that is neither scaled nor capped."""
+
+    def qkv_norm_write(self, qkv, bias, step: StepTensors, kv: KvSlot | None, rotary: RotaryTable | None,
+                       num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int, norm_eps: float | None,
+                       q_weight, k_weight, q_temp, q_out) -> None:
+        """``qkv`` is the float32 projection ``[T, heads * head_dim + kv_heads * (head_dim + value_dim)]`` (or the
+        slices of a split product; more columns behind these are not read) and ``bias`` its float32 bias or None.
+        With ``norm_eps`` every head of q and k is divided by its root mean square over ``head_dim`` (eps inside
+        the root) and, with ``q_weight`` / ``k_weight`` (float32 ``[head_dim]``), multiplied by it; THEN q and k are
+        rotated (``rotary``); with ``q_temp = (coef, every)`` q at position p is multiplied by
+        ``1 + coef * ln(floor((p + 1) / every) + 1)``.  k and v go to their pages (if ``kv``; values may have
+        another size than keys) and q to ``q_out [T, heads * head_dim]`` in the set's dtype.  All float32."""
+        raise NotImplementedError
 
     # -- norms around a sublayer, keys that are their own values, routed feed-forwards -----------------------------
     def norm_add_rmsnorm(self, delta, delta_weight, delta_eps: float, residual, weight, eps: float, out,
@@ -248,7 +262,7 @@ class KernelSet(ABC):
         raise NotImplementedError
 
     def route_top(self, x, router, top: int, scoring: str = "sigmoid", groups: tuple[int, int] | None = None,
-                  weight_scale: float = 1.0, extra_rows: int = 0):
+                  weight_scale: float = 1.0, extra_rows: int = 0, correction=None, normalise: bool = False):
         """The ``top`` experts of every token: logits ``x @ router.T`` (``router [experts, hidden]``) accumulated in
         float32 -> ``(ids [T, top] int32, weights [T, top] float32)``, ``weights`` the chosen experts' scores
         (``sigmoid(logit)``, not renormalised) times ``weight_scale``, the largest first, ties to the lower index.
@@ -257,15 +271,22 @@ class KernelSet(ABC):
         sum of its two largest scores (of its one score, for groups of one), and only experts of the ``keep`` groups
         with the largest scores (ties to the lower group) can be chosen.  With ``extra_rows`` the router matrix has
         that many more rows below the experts', which are no experts: their float32 logits ``[T, extra_rows]`` are
-        returned as a third value (a gate that reads the same input, made in the same pass)."""
+        returned as a third value (a gate that reads the same input, made in the same pass).
+
+        ``scoring="softmax"``: the scores are a softmax over all experts' logits.  ``correction [experts]``
+        (float32) is added to the scores for the choice only; the weights are the plain scores.  ``normalise``:
+        the chosen scores are divided by their sum (+ 1e-20) before ``weight_scale``."""
         raise NotImplementedError
 
-    def routed_swiglu(self, x, ids, weights, gate_up, down, scale_input: bool = True, limit: float | None = None):
+    def routed_swiglu(self, x, ids, weights, gate_up, down, scale_input: bool = True, limit: float | None = None,
+                      identity: int = 0):
         """Every token through its chosen experts: ``gate_up [experts, 2 ff, hidden]`` (gate rows, then up rows),
         ``down [experts, hidden, ff]``; expert e of pair (t, j) computes ``down_e (silu(gate_e z) * (up_e z))`` with
         ``z = weights[t, j] * x[t]`` (``scale_input``) or on ``x[t]`` with the result times the weight.  With a
         ``limit`` the hidden activation is the capped form of :meth:`linear_glu`.  Returns
-        float32 slices ``[top, T, hidden]`` whose sum over the first axis is the routed output."""
+        float32 slices ``[top, T, hidden]`` whose sum over the first axis is the routed output.  With ``identity = n``
+        ids ``experts .. experts + n - 1`` stand for experts that return their input: such a pair's slice row is
+        ``weights[t, j] * x[t]`` (``scale_input`` False only)."""
         raise NotImplementedError
 
     def linear_glu(self, x, weight, limit: float | None = None, row_gate=None):
@@ -331,14 +352,17 @@ class KernelSet(ABC):
         raise NotImplementedError
 
     def head_gate(self, x, logits, num_heads: int) -> None:
-        """x ``[T, heads * d]`` in place: head h of token t times sigmoid(logits[t, h]) (float32 logits, or slices)."""
+        """x ``[T, heads * d]`` in place: head h of token t times sigmoid(logits[t, h]) (float32 logits, or slices).
+        With ``num_heads`` the number of columns (``d = 1``) the gate is element by element."""
         raise NotImplementedError
 
-    def short_conv(self, x, weight, bias, state, step: StepTensors, activation: str = "silu"):
+    def short_conv(self, x, weight, bias, state, step: StepTensors, activation: str = "silu", input_bias=None):
         """Causal convolution over time, per channel and per request: ``x [T, C]`` float32 (any row stride; or slices),
         ``weight [C, taps]`` whose last column multiplies the current token, ``state [seats, taps - 1, C]`` the
         request's last inputs (oldest first; zeros at a request's start), which the call moves on by the
-        step's tokens.  Returns float32 ``[T, C]`` after the activation (``"silu"`` or ``"none"``)."""
+        step's tokens.  Returns float32 ``[T, C]`` after the activation (``"silu"`` or ``"none"``).  ``input_bias [C]``
+        (float32) is added to every input of the step before anything else (the state holds the sums; before a
+        request's start the inputs are zeros, not the bias)."""
         raise NotImplementedError
 
     def linear_recurrence(self, rule: str, q, k, v, decay, write, state, step: StepTensors, heads: int, groups: int,

@@ -1,6 +1,6 @@
 """Architecture recipes (registered on import) and the decoder they build."""
 
-from . import fovudra, qwen2, zelasun, zururax  # noqa: F401
+from . import fovudra, qwen2, zelasun, zururax, zuzunex  # noqa: F401
 from .decoder import DecoderModel, model_tensor_specs, slot_needs
 
 __all__ = ["DecoderModel", "model_tensor_specs", "slot_needs"]

@@ -7,7 +7,12 @@ pairs ``(j, j + d/2)`` (rotate-half).  ``rotary_dim < head_dim``, interleaved pa
 a factor on cos and sin are parameters for other layer kinds, and so is ``scaling``, which divides the
 frequencies of long waves: with wavelength ``l = 2 pi / f``, ``f`` stays where ``l < original / high``, becomes
 ``f / factor`` where ``l > original / low``, and in between ``(1 - s) f / factor + s f`` with
-``s = (original / l - low) / (high - low)``.  ``none`` rotates nothing.
+``s = (original / l - low) / (high - low)``.  A ``scaling`` with the keys ``fast`` and ``slow`` instead of ``low`` and
+``high`` blends over the pair index: with ``index(t) = d ln(original / (2 pi t)) / (2 ln theta)`` (the pair that turns
+``t`` times over ``original`` positions), ``lo = max(floor(index(fast)), 0)``, ``hi = min(ceil(index(slow)), d - 1)``
+and ``r_j = clamp((j - lo) / max(hi - lo, 0.001), 0, 1)`` the frequency of pair ``j`` is ``r_j f / factor + (1 - r_j) f``
+(:func:`ramped_frequencies`); such encodings usually also put ``0.1 ln(factor) + 1`` on cos and sin (``factor`` of the
+encoding, given by the recipe).  ``none`` rotates nothing.
 
 An encoding that is no table of frequencies (learned or additive positions, a rotation
 that depends on more than the position) returns ``None`` from ``rotary_table()`` and
@@ -42,10 +47,26 @@ def scaled_frequencies(theta: float, rotary_dim: int, factor: float, low: float,
     return out.to(torch.float32)
 
 
+def ramped_frequencies(theta: float, rotary_dim: int, factor: float, original: float, fast: float, slow: float) -> torch.Tensor:
+    """Rotary frequencies ``theta**(-2j / d)``, slowed by ``factor`` along a ramp over the pair index that starts at the
+    pair turning ``fast`` times over ``original`` positions and ends at the one turning ``slow`` times; made in
+    float64 and stored as float32."""
+    j = torch.arange(0, rotary_dim // 2, dtype=torch.float64)
+    freq = theta ** (-2.0 * j / rotary_dim)
+
+    def index_of(turns: float) -> float:
+        return rotary_dim * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(theta))
+
+    lo = max(math.floor(index_of(fast)), 0)
+    hi = min(math.ceil(index_of(slow)), rotary_dim - 1)
+    ramp = ((j - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+    return (freq / factor * ramp + freq * (1.0 - ramp)).to(torch.float32)
+
+
 @POSITION_ENCODINGS.register("rotary")
 class RotaryEncoding:
     """params: ``head_dim``, ``theta``, optional ``rotary_dim``, ``interleaved``, ``factor``, ``scaling``
-    (a mapping with ``factor``, ``low``, ``high``, ``original``)."""
+    (a mapping with ``factor``, ``original`` and either ``low``, ``high`` or ``fast``, ``slow``)."""
 
     def __init__(self, table: RotaryTable) -> None:
         self._table = table
@@ -58,15 +79,19 @@ class RotaryEncoding:
         if rotary_dim % 2 or rotary_dim > head_dim:
             raise ValueError(f"rotary_dim {rotary_dim} must be even and at most head_dim {head_dim}")
         scaling = spec.params.get("scaling")
-        scaled = tuple(float(scaling[n]) for n in ("factor", "low", "high", "original")) if scaling else None
+        by_turns = bool(scaling) and "fast" in scaling
+        names = ("factor", "original", "fast", "slow") if by_turns else ("factor", "low", "high", "original")
+        scaled = tuple(float(scaling[n]) for n in names) + (by_turns,) if scaling else None
         key = (theta, rotary_dim, bool(spec.params.get("interleaved", False)), float(spec.params.get("factor", 1.0)),
                str(ctx.device), scaled)
         table = _TABLES.get(key)
         if table is None:
             if scaled is None:
                 inv_freq = 1.0 / (theta ** (torch.arange(0, rotary_dim, 2, dtype=torch.float32) / rotary_dim))
+            elif by_turns:
+                inv_freq = ramped_frequencies(theta, rotary_dim, *scaled[:4])
             else:
-                inv_freq = scaled_frequencies(theta, rotary_dim, *scaled)
+                inv_freq = scaled_frequencies(theta, rotary_dim, *scaled[:4])
             table = _TABLES[key] = RotaryTable(inv_freq.to(ctx.device), *key[1:4])
         return cls(table)
 

@@ -9,7 +9,10 @@ be chosen.  An expert is ``down(silu(gate h) * (up h))`` or, with a ``limit``, t
 ``g = min(gate h, limit)``, ``u = clamp(up h, -limit, limit)``, ``down(g * sigmoid(1.702 g) * (u + 1))``.
 A shared expert of the same form (with a limit of its own) runs for every token and is added; with
 ``shared_gate`` it is first multiplied by ``sigmoid(w_sg . h)``, one number per token, whose logit is made
-in the router's pass (``w_sg`` is one more row below the router's).  The output stays a sum still to be done
+in the router's pass (``w_sg`` is one more row below the router's).  ``scoring="softmax"`` takes the scores as a
+softmax over all router outputs; ``correction`` names a vector (``[router outputs]``) that is added to the scores for
+the choice only; ``normalise`` divides the chosen scores by their sum (+ 1e-20); with ``identity = n`` the router has
+``n`` more outputs than there are experts, which stand for experts without tensors that return their input.  The output stays a sum still to be done
 (the routed slices and the shared expert's), which the norm kernel that follows adds up.
 """
 
@@ -28,8 +31,10 @@ class RoutedSwiGlu:
     """params: ``experts``, ``top``, ``intermediate_size``, ``shared_size`` (None: no shared expert), optional
     ``weight_on`` (``"input"``, default, or ``"output"``), ``weight_scale`` (default 1), ``groups`` (``(count,
     keep)`` or None), ``limit`` and ``shared_limit`` (None: SwiGLU), ``shared_gate`` (None, or what the name of
-    the shared expert's gate vector adds to ``shared.``).
-    tensors (prefix +): ``router [experts, hidden]``; ``e<j>.gate, e<j>.up [ff, hidden]``, ``e<j>.down [hidden, ff]``;
+    the shared expert's gate vector adds to ``shared.``), ``scoring`` (``"sigmoid"``, default, or ``"softmax"``),
+    ``correction`` (None, or the name of the vector added to the scores for the choice), ``normalise`` (bool) and
+    ``identity`` (0: how many router outputs behind the experts' return their input).
+    tensors (prefix +): ``router [experts + identity, hidden]``; ``<correction> [experts + identity]``; ``e<j>.gate, e<j>.up [ff, hidden]``, ``e<j>.down [hidden, ff]``;
     ``shared.gate, shared.up, shared.down``; ``shared.<shared_gate> [1, hidden]``."""
 
     graph_safe = True
@@ -44,13 +49,24 @@ class RoutedSwiGlu:
         self.limit = float(prm["limit"]) if prm.get("limit") is not None else None
         self.shared_limit = float(prm["shared_limit"]) if prm.get("shared_limit") is not None else None
         self.gated_shared = bool(prm.get("shared_gate")) and shared_gate_up is not None  # the gate's row lies below the router's
+        self.scoring = prm.get("scoring", "sigmoid")
+        self.normalise = bool(prm.get("normalise"))
+        self.identity = int(prm.get("identity") or 0)
+        self.correction = None  # set by build
         self.kernels = kernels
 
     @staticmethod
     def _check(prm) -> None:
         experts, top = int(prm["experts"]), int(prm["top"])
-        if experts < 1 or top < 1 or top > experts or top > 32:
-            raise ValueError(f"experts {experts}, top {top}: 1 <= top <= min(experts, 32)")
+        identity = int(prm.get("identity") or 0)
+        if experts < 1 or top < 1 or identity < 0 or top > experts + identity or top > 32:
+            raise ValueError(f"experts {experts} (+ {identity} that return their input), top {top}: 1 <= top <= min(outputs, 32)")
+        if prm.get("scoring", "sigmoid") not in ("sigmoid", "softmax"):
+            raise ValueError(f"scoring {prm['scoring']!r}: 'sigmoid' or 'softmax'")
+        if (identity or prm.get("correction")) and (prm.get("groups") or prm.get("shared_gate")):
+            raise ValueError("identity experts and a correction do not go with groups or a gated shared expert")
+        if identity and prm.get("weight_on", "input") != "output":
+            raise ValueError("identity experts go with weight_on='output'")
         if prm.get("weight_on", "input") not in ("input", "output"):
             raise ValueError(f"weight_on {prm['weight_on']!r}: 'input' or 'output'")
         if prm.get("groups"):
@@ -73,7 +89,10 @@ class RoutedSwiGlu:
         for e in range(int(prm["experts"])):
             specs += [TensorSpec(f"{p}e{e}.gate", (ff, hidden_size)), TensorSpec(f"{p}e{e}.up", (ff, hidden_size)),
                       TensorSpec(f"{p}e{e}.down", (hidden_size, ff))]
-        specs.append(TensorSpec(p + "router", (int(prm["experts"]), hidden_size)))
+        outputs = int(prm["experts"]) + int(prm.get("identity") or 0)
+        specs.append(TensorSpec(p + "router", (outputs, hidden_size)))
+        if prm.get("correction"):
+            specs.append(TensorSpec(p + prm["correction"], (outputs,), "bias"))
         if prm.get("shared_size") is not None:
             shared = int(prm["shared_size"])
             specs += [TensorSpec(p + "shared.gate", (shared, hidden_size)), TensorSpec(p + "shared.up", (shared, hidden_size)),
@@ -96,13 +115,20 @@ class RoutedSwiGlu:
         router = w.matrix(p + "router")
         if prm.get("shared_gate") and shared_gate_up is not None:
             router = fuse_rows([router, w.matrix(f"{p}shared.{prm['shared_gate']}")])
-        return cls(router, gate_up, down, shared_gate_up, shared_down, dict(prm), ctx.kernels)
+        part = cls(router, gate_up, down, shared_gate_up, shared_down, dict(prm), ctx.kernels)
+        if prm.get("correction"):
+            part.correction = w.vector(p + prm["correction"])
+        return part
 
     def forward(self, x: torch.Tensor, run: LayerRun):
         k = self.kernels
         plain = self.groups is None and self.weight_scale == 1.0 and self.limit is None and not self.gated_shared
 
         def routed():
+            if self.scoring != "sigmoid" or self.correction is not None or self.normalise or self.identity:
+                ids, weights = k.route_top(x, self.router, self.top, self.scoring, None, self.weight_scale, 0,
+                                           self.correction, self.normalise)
+                return k.routed_swiglu(x, ids, weights, self.gate_up, self.down, self.scale_input, self.limit, self.identity)
             if plain:
                 ids, weights = k.route_top(x, self.router, self.top, "sigmoid")
                 return k.routed_swiglu(x, ids, weights, self.gate_up, self.down, self.scale_input)

@@ -88,7 +88,7 @@ def rope_kv_write(qkv, step: StepTensors, kv: KvSlot | None, rotary, num_heads, 
 
 
 def attention(qkv, step: StepTensors, kv: KvSlot, num_heads, num_kv_heads, head_dim, window, scale, chunk=None,
-              keep_first=0):
+              keep_first=0, softcap=0.0, sink=None):
     """Token by token: gather the visible keys of the token's request from its pages, softmax in float32."""
     tokens = step.num_tokens
     out = torch.zeros((tokens, num_heads * kv.v.shape[-1]), dtype=qkv.dtype, device=qkv.device)
@@ -111,7 +111,11 @@ def attention(qkv, step: StepTensors, kv: KvSlot, num_heads, num_kv_heads, head_
         k = k.repeat_interleave(rep, dim=1)
         v = v.repeat_interleave(rep, dim=1)
         scores = torch.einsum("hd,nhd->hn", q, k) * scale
-        probs = torch.softmax(scores, dim=-1)
+        if softcap and softcap > 0:
+            scores = float(softcap) * torch.tanh(scores / float(softcap))
+        if sink is not None:  # one more term in the denominator: a column that carries no value
+            scores = torch.cat([scores, sink.float().reshape(num_heads, 1)], dim=-1)
+        probs = torch.softmax(scores, dim=-1)[:, : keys.numel()]
         out[t] = torch.einsum("hn,nhd->hd", probs, v).reshape(-1).to(qkv.dtype)
     return out
 
@@ -164,10 +168,12 @@ def _softplus(z):
     return torch.log1p(torch.exp(-z.abs())) + torch.clamp(z, min=0)
 
 
-def short_conv(x, weight, bias, state, step: StepTensors, activation="silu"):
+def short_conv(x, weight, bias, state, step: StepTensors, activation="silu", input_bias=None):
     """Token by token in the step's order: the request's window of inputs lives in ``state[seat]``."""
     tokens, taps = step.num_tokens, weight.shape[1]
     x = whole(x)
+    if input_bias is not None:
+        x = x + input_bias.float()
     seats = token_seats(step)
     out = torch.zeros((tokens, x.shape[1]), dtype=torch.float32, device=x.device)
     for t in range(tokens):
@@ -277,6 +283,39 @@ def qk_rope_norm_write(qk, bias, step: StepTensors, kv: KvSlot | None, rotary, n
     return q.reshape(tokens, num_heads * head_dim).to(q_dtype)
 
 
+def qkv_norm_write(qkv, bias, step: StepTensors, kv: KvSlot | None, rotary, num_heads, num_kv_heads, head_dim, value_dim,
+                   norm_eps, q_weight, k_weight, q_temp, q_dtype):
+    """Returns q [T, heads * head_dim]; stores k (normed, rotated) and v in their pages."""
+    tokens = step.num_tokens
+    q_end, k_end = num_heads * head_dim, (num_heads + num_kv_heads) * head_dim
+    dense = whole(qkv)[:tokens, : k_end + num_kv_heads * value_dim]
+    if bias is not None:
+        dense = dense + bias.float()
+    positions = step.positions[:tokens]
+    q = dense[:, :q_end].reshape(tokens, num_heads, head_dim)
+    k = dense[:, q_end:k_end].reshape(tokens, num_kv_heads, head_dim)
+    v = dense[:, k_end:].reshape(tokens, num_kv_heads, value_dim)
+    if norm_eps is not None:
+        q = q * torch.rsqrt((q * q).mean(-1, keepdim=True) + norm_eps)
+        k = k * torch.rsqrt((k * k).mean(-1, keepdim=True) + norm_eps)
+        if q_weight is not None:
+            q = q * q_weight.float()
+        if k_weight is not None:
+            k = k * k_weight.float()
+    q, k = rotate(q, positions, rotary), rotate(k, positions, rotary)
+    if q_temp is not None:
+        steps = torch.div(positions + 1, int(q_temp[1]), rounding_mode="floor").float()
+        q = q * (1.0 + float(q_temp[0]) * torch.log(steps + 1.0))[:, None, None]
+    if kv is not None:
+        pos = positions.long()
+        pages = kv.block_table[token_seats(step), pos // kv.page_size].long()
+        if bool(((pages < 0) | (pages >= kv.num_pages)).any()):
+            raise IndexError("a new token's page is missing from its block table")
+        kv.k[pages, :, pos % kv.page_size, :] = k.to(kv.k.dtype)
+        kv.v[pages, :, pos % kv.page_size, :] = v.to(kv.v.dtype)
+    return q.reshape(tokens, q_end).to(q_dtype)
+
+
 def activation(x, kind="silu", scale=1.0, scaled_columns=0):
     out = whole(x).clone()
     if kind == "silu":
@@ -340,10 +379,19 @@ def glu(g, u, limit=None):
     return g * torch.sigmoid(1.702 * g) * (u + 1.0)
 
 
-def route_top(x, router, top, scoring="sigmoid", groups=None, weight_scale=1.0, extra_rows=0):
+def route_top(x, router, top, scoring="sigmoid", groups=None, weight_scale=1.0, extra_rows=0, correction=None,
+              normalise=False):
     logits = x.float() @ router.float().T
     experts = router.shape[0] - int(extra_rows)
-    scores = torch.sigmoid(logits[:, :experts])
+    scores = torch.softmax(logits[:, :experts], -1) if scoring == "softmax" else torch.sigmoid(logits[:, :experts])
+    if correction is not None or normalise:
+        choice = scores + correction.float() if correction is not None else scores
+        ids = torch.sort(choice, dim=-1, descending=True, stable=True).indices[:, :top]
+        weights = torch.gather(scores, 1, ids)
+        if normalise:
+            weights = weights / (weights.sum(-1, keepdim=True) + 1e-20)
+        out = ids.to(torch.int32).contiguous(), (weights * float(weight_scale)).contiguous()
+        return out if not extra_rows else (*out, logits[:, experts:].contiguous())
     allowed = scores.clone()
     if groups is not None and groups[0] > 1 and groups[1] < groups[0]:
         count, keep = int(groups[0]), int(groups[1])
@@ -358,13 +406,16 @@ def route_top(x, router, top, scoring="sigmoid", groups=None, weight_scale=1.0, 
     return out if not extra_rows else (*out, logits[:, experts:].contiguous())
 
 
-def routed_swiglu(x, ids, weights, gate_up, down, scale_input=True, limit=None):
+def routed_swiglu(x, ids, weights, gate_up, down, scale_input=True, limit=None, identity=0):
     tokens, top = ids.shape
     ff = gate_up.shape[1] // 2
     out = torch.zeros((top, tokens, x.shape[1]), dtype=torch.float32, device=x.device)
     for t in range(tokens):
         for j in range(top):
             e, w = int(ids[t, j]), weights[t, j].float()
+            if gate_up.shape[0] <= e < gate_up.shape[0] + identity:  # an expert that returns its input
+                out[j, t] = x[t].float() * w
+                continue
             z = (x[t].float() * w).to(x.dtype).float() if scale_input else x[t].float()
             both = gate_up[e].float() @ z
             hidden = glu(both[:ff], both[ff:], limit).to(x.dtype).float()
@@ -489,8 +540,14 @@ class RefKernels(KernelSet):
     def rope_kv_write(self, qkv, step, kv, rotary, num_heads, num_kv_heads, head_dim, bias=None, q_out=None):
         rope_kv_write(qkv, step, kv, rotary, num_heads, num_kv_heads, head_dim, bias, q_out)
 
-    def attention(self, qkv, out, step, kv, num_heads, num_kv_heads, head_dim, window, scale, chunk=None, keep_first=0):
-        out.copy_(attention(qkv, step, kv, num_heads, num_kv_heads, head_dim, window, scale, chunk, keep_first))
+    def attention(self, qkv, out, step, kv, num_heads, num_kv_heads, head_dim, window, scale, chunk=None, keep_first=0,
+                  softcap=0.0, sink=None):
+        out.copy_(attention(qkv, step, kv, num_heads, num_kv_heads, head_dim, window, scale, chunk, keep_first, softcap, sink))
+
+    def qkv_norm_write(self, qkv, bias, step, kv, rotary, num_heads, num_kv_heads, head_dim, value_dim, norm_eps,
+                       q_weight, k_weight, q_temp, q_out):
+        q_out.copy_(qkv_norm_write(qkv, bias, step, kv, rotary, num_heads, num_kv_heads, head_dim, value_dim, norm_eps,
+                                   q_weight, k_weight, q_temp, q_out.dtype))
 
     def norm_add_rmsnorm(self, delta, delta_weight, delta_eps, residual, weight, eps, out, rows_index=None):
         new_residual, normed = norm_add_rmsnorm(delta, delta_weight, delta_eps, residual, weight, eps,
@@ -512,11 +569,12 @@ class RefKernels(KernelSet):
     def stabilized_readout(self, read, floor, heads, value_dim):
         return stabilized_readout(read, floor, heads, value_dim)
 
-    def route_top(self, x, router, top, scoring="sigmoid", groups=None, weight_scale=1.0, extra_rows=0):
-        return route_top(x, router, top, scoring, groups, weight_scale, extra_rows)
+    def route_top(self, x, router, top, scoring="sigmoid", groups=None, weight_scale=1.0, extra_rows=0, correction=None,
+                  normalise=False):
+        return route_top(x, router, top, scoring, groups, weight_scale, extra_rows, correction, normalise)
 
-    def routed_swiglu(self, x, ids, weights, gate_up, down, scale_input=True, limit=None):
-        return routed_swiglu(x, ids, weights, gate_up, down, scale_input, limit)
+    def routed_swiglu(self, x, ids, weights, gate_up, down, scale_input=True, limit=None, identity=0):
+        return routed_swiglu(x, ids, weights, gate_up, down, scale_input, limit, identity)
 
     def linear_glu(self, x, weight, limit=None, row_gate=None):
         return linear_glu(x, weight, self.dtype, limit, row_gate)
@@ -548,8 +606,8 @@ class RefKernels(KernelSet):
     def head_gate(self, x, logits, num_heads):
         x.copy_(head_gate(x, logits, num_heads))
 
-    def short_conv(self, x, weight, bias, state, step, activation="silu"):
-        return short_conv(x, weight, bias, state, step, activation)
+    def short_conv(self, x, weight, bias, state, step, activation="silu", input_bias=None):
+        return short_conv(x, weight, bias, state, step, activation, input_bias)
 
     def linear_recurrence(self, rule, q, k, v, decay, write, state, step, heads, groups, key_dim, value_dim,
                           decay_rate=None, decay_bias=None, skip=None, unit_column=False):
