@@ -45,7 +45,7 @@ attention_decode_kernel(const T* __restrict__ q, int q_row_stride, T* __restrict
                         const int* __restrict__ positions, const int* __restrict__ token_seq,
                         const int* __restrict__ seq_seat, const int* __restrict__ block_table, int table_width,
                         const T* __restrict__ k_cache, const T* __restrict__ v_cache, int num_heads, int group_size,
-                        int head_chunks, int num_kv_heads, int page_size, int num_pages, int window, int key_chunk, int keep_first, float scale,
+                        int head_chunks, int num_kv_heads, int page_size, int num_pages, int window, int key_chunk, int keep_first, float scale, float softcap, const float* sink,
                         int* __restrict__ error) {
   constexpr int HEAD_DIM = DL * 8;
   constexpr int ROWS_PER_WARP = 32 / DL;
@@ -133,7 +133,7 @@ attention_decode_kernel(const T* __restrict__ q, int q_row_stride, T* __restrict
         }
 #pragma unroll
         for (int offset = DL / 2; offset > 0; offset >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, offset);
-        s[g] = dot * scale;
+        s[g] = cap_score(dot * scale, softcap);
       }
       if (live[u]) {
 #pragma unroll
@@ -172,7 +172,8 @@ attention_decode_kernel(const T* __restrict__ q, int q_row_stride, T* __restrict
     }
     const int head = head0 + g;
     if (num_splits == 1) {
-      out[(size_t)t * out_row_stride + (size_t)head * HEAD_DIM + e] = from_float<T>(l_all > 0.f ? o / l_all : 0.f);
+      const float inv = sink ? sink_inverse(m_all, l_all, sink[head]) : (l_all > 0.f ? 1.f / l_all : 0.f);
+      out[(size_t)t * out_row_stride + (size_t)head * HEAD_DIM + e] = from_float<T>(o * inv);
     } else {
       const size_t row = ((size_t)t * num_heads + head) * num_splits + split;
       scratch_o[row * HEAD_DIM + e] = o;
@@ -188,7 +189,8 @@ template <typename T>
 __global__ void __launch_bounds__(128)
 attention_decode_merge_kernel(const float* __restrict__ scratch_o,
                                               const float* __restrict__ scratch_ml, T* __restrict__ out,
-                                              int out_row_stride, int num_heads, int head_dim, int num_splits) {
+                                              int out_row_stride, int num_heads, int head_dim, int num_splits,
+                                              const float* __restrict__ sink) {
   const int t = blockIdx.x, head = blockIdx.y;
   const size_t row0 = ((size_t)t * num_heads + head) * num_splits;
   float m_all = -INFINITY;
@@ -201,7 +203,8 @@ attention_decode_merge_kernel(const float* __restrict__ scratch_o,
       l_all += scratch_ml[(row0 + s) * 2 + 1] * w;
       o += scratch_o[(row0 + s) * head_dim + e] * w;
     }
-    out[(size_t)t * out_row_stride + (size_t)head * head_dim + e] = from_float<T>(l_all > 0.f ? o / l_all : 0.f);
+    const float inv = sink ? sink_inverse(m_all, l_all, sink[head]) : (l_all > 0.f ? 1.f / l_all : 0.f);
+    out[(size_t)t * out_row_stride + (size_t)head * head_dim + e] = from_float<T>(o * inv);
   }
 }
 
@@ -209,7 +212,7 @@ template <typename T, int DL>
 int launch_decode(const void* q, int q_row_stride, void* out, int out_row_stride, float* scratch_o,
                   float* scratch_ml, const int* positions, const int* token_seq, const int* seq_seat,
                   const int* block_table, int table_width, const void* k_cache, const void* v_cache, int tokens,
-                  int num_heads, int num_kv_heads, int page_size, int num_pages, int window, int key_chunk, int keep_first, float scale,
+                  int num_heads, int num_kv_heads, int page_size, int num_pages, int window, int key_chunk, int keep_first, float scale, float softcap, const float* sink,
                   int num_splits, int* error, cudaStream_t stream) {
   const int group = num_heads / num_kv_heads;
   // Heads of one kv head are handled GC at a time; pick the chunk that wastes least.
@@ -224,7 +227,7 @@ int launch_decode(const void* q, int q_row_stride, void* out, int out_row_stride
   attention_decode_kernel<T, DL, GCV><<<grid, kDecodeThreads, 0, stream>>>(                                      \
       (const T*)q, q_row_stride, (T*)out, out_row_stride, scratch_o, scratch_ml, positions, token_seq, seq_seat, \
       block_table, table_width, (const T*)k_cache, (const T*)v_cache, num_heads, group, chunks, num_kv_heads,    \
-      page_size, num_pages, window, key_chunk, keep_first, scale, error)
+      page_size, num_pages, window, key_chunk, keep_first, scale, softcap, sink, error)
   switch (gc) {
     case 1: DISTIE_DECODE_CASE(1); break;
     case 2: DISTIE_DECODE_CASE(2); break;
@@ -237,7 +240,7 @@ int launch_decode(const void* q, int q_row_stride, void* out, int out_row_stride
   if (num_splits > 1) {
     const dim3 merge_grid(tokens, num_heads);
     attention_decode_merge_kernel<T><<<merge_grid, DL * 8 >= 128 ? 128 : 64, 0, stream>>>(
-        scratch_o, scratch_ml, (T*)out, out_row_stride, num_heads, DL * 8, num_splits);
+        scratch_o, scratch_ml, (T*)out, out_row_stride, num_heads, DL * 8, num_splits, sink);
     DISTIE_LAUNCH_CHECK();
   }
   return 0;
@@ -248,11 +251,11 @@ int dispatch_decode(int head_dim, const void* q, int q_row_stride, void* out, in
                     float* scratch_o, float* scratch_ml, const int* positions, const int* token_seq,
                     const int* seq_seat, const int* block_table, int table_width, const void* k_cache,
                     const void* v_cache, int tokens, int num_heads, int num_kv_heads, int page_size, int num_pages,
-                    int window, int key_chunk, int keep_first, float scale, int num_splits, int* error, cudaStream_t stream) {
+                    int window, int key_chunk, int keep_first, float scale, float softcap, const float* sink, int num_splits, int* error, cudaStream_t stream) {
 #define DISTIE_DECODE_DIM(DLV)                                                                                   \
   return launch_decode<T, DLV>(q, q_row_stride, out, out_row_stride, scratch_o, scratch_ml, positions, token_seq, \
                                seq_seat, block_table, table_width, k_cache, v_cache, tokens, num_heads,          \
-                               num_kv_heads, page_size, num_pages, window, key_chunk, keep_first, scale, num_splits, error, stream)
+                               num_kv_heads, page_size, num_pages, window, key_chunk, keep_first, scale, softcap, sink, num_splits, error, stream)
   switch (head_dim) {
     case 16: DISTIE_DECODE_DIM(2);
     case 32: DISTIE_DECODE_DIM(4);
@@ -279,7 +282,7 @@ extern "C" int distie_attention_decode(const void* q, int q_row_stride, void* ou
                                        const int* seq_seat, const int* block_table, int table_width,
                                        const void* k_cache, const void* v_cache, int tokens, int num_heads,
                                        int num_kv_heads, int head_dim, int page_size, int num_pages, int window, int key_chunk,
-                                       int keep_first, float scale, int num_splits, int dtype, int* error, cudaStream_t stream) {
+                                       int keep_first, float scale, float softcap, const float* sink, int num_splits, int dtype, int* error, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (num_heads < 1 || num_kv_heads < 1 || num_heads % num_kv_heads != 0 || page_size < 1 || table_width < 1 ||
       num_splits < 1 || num_splits > 65535 || (num_splits > 1 && scratch == nullptr) || keep_first < 0)
@@ -290,11 +293,11 @@ extern "C" int distie_attention_decode(const void* q, int q_row_stride, void* ou
     return dispatch_decode<__nv_bfloat16>(head_dim, q, q_row_stride, out, out_row_stride, scratch_o, scratch_ml,
                                           positions, token_seq, seq_seat, block_table, table_width, k_cache, v_cache,
                                           tokens, num_heads, num_kv_heads, page_size, num_pages, window, key_chunk, keep_first, scale,
-                                          num_splits, error, stream);
+                                          softcap, sink, num_splits, error, stream);
   if (dtype == DISTIE_F32)
     return dispatch_decode<float>(head_dim, q, q_row_stride, out, out_row_stride, scratch_o, scratch_ml, positions,
                                   token_seq, seq_seat, block_table, table_width, k_cache, v_cache, tokens, num_heads,
-                                  num_kv_heads, page_size, num_pages, window, key_chunk, keep_first, scale, num_splits, error, stream);
+                                  num_kv_heads, page_size, num_pages, window, key_chunk, keep_first, scale, softcap, sink, num_splits, error, stream);
   return DISTIE_ERR_UNSUPPORTED;
 }
 
@@ -363,5 +366,5 @@ extern "C" int distie_attention_decode_static(const void* q, int q_row_stride, v
   // (max, sum, mix) of every (token, head, split) before the merge kernel reads it.
   return distie_attention_decode(q, q_row_stride, out, out_row_stride, scratch, positions, token_seq, seq_seat,
                                  block_table, table_width, k_cache, v_cache, tokens, num_heads, num_kv_heads, head_dim,
-                                 page_size, num_pages, window, /*key_chunk=*/0, /*keep_first=*/0, scale, num_splits, dtype, error, stream);
+                                 page_size, num_pages, window, /*key_chunk=*/0, /*keep_first=*/0, scale, /*softcap=*/0.f, /*sink=*/nullptr, num_splits, dtype, error, stream);
 }

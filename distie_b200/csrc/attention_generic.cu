@@ -3,7 +3,8 @@
 // One block per (token, query head).  The token at position `pos` of its request
 // sees the keys `max(0, pos - window + 1) .. pos` of that request (window <= 0:
 // all of them; chunk > 0: only those of its own chunk of that many positions; keep_first > 0: also the
-// request's first that-many keys when the window has moved past them),
+// request's first that-many keys when the window has moved past them; softcap > 0: a scaled score s becomes
+// softcap * tanh(s / softcap); sink: one float per head whose exponential joins the softmax's denominator),
 // which by then are all in the cache: earlier steps stored the older
 // ones and this step's write kernel ran before.  Nothing but the token's position,
 // its request's seat and the block table decides what is read, so the result does
@@ -27,7 +28,8 @@ attention_generic_kernel(const T* __restrict__ q, int q_row_stride, T* __restric
                          const int* __restrict__ seq_seat, const int* __restrict__ block_table, int table_width,
                          const T* __restrict__ k_cache, const T* __restrict__ v_cache, int group_size,
                          int num_kv_heads, int head_dim, int value_dim, int page_size, int num_pages, int window,
-                         int chunk, int keep_first, float scale, int* __restrict__ error) {
+                         int chunk, int keep_first, float scale, float softcap, const float* __restrict__ sink,
+                         int* __restrict__ error) {
   __shared__ float sh_m[kGenericWarps], sh_l[kGenericWarps];
   __shared__ float sh_acc[kGenericWarps][kMaxHeadDim];
   const int t = blockIdx.x, head = blockIdx.y;
@@ -65,7 +67,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_row_stride, T* __restric
       const int e = lane + 32 * i;
       if (e < head_dim) dot += qv[i] * to_float(k_cache[base + e]);
     }
-    const float s = warp_sum(dot) * scale;  // scaled after the product, as the reference does
+    const float s = cap_score(warp_sum(dot) * scale, softcap);  // scaled after the product, as the reference does
     const float m_new = fmaxf(m, s);
     const float corr = expf(m - m_new);
     const float p = expf(s - m_new);
@@ -94,7 +96,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_row_stride, T* __restric
     weight[w] = sh_m[w] == -INFINITY ? 0.f : expf(sh_m[w] - m_all);
     l_all += sh_l[w] * weight[w];
   }
-  const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+  const float inv = sink ? sink_inverse(m_all, l_all, sink[head]) : (l_all > 0.f ? 1.f / l_all : 0.f);
   T* out_row = out + (size_t)t * out_row_stride + (size_t)head * value_dim;
   for (int e = threadIdx.x; e < value_dim; e += blockDim.x) {
     float total = 0.f;
@@ -113,8 +115,8 @@ extern "C" int distie_attention_generic(const void* q, int q_row_stride, void* o
                                         const int* block_table, int table_width, const void* k_cache,
                                         const void* v_cache, int tokens, int num_heads, int num_kv_heads,
                                         int head_dim, int value_dim, int page_size, int num_pages, int window,
-                                        int chunk, int keep_first, float scale, int dtype, int* error,
-                                        cudaStream_t stream) {
+                                        int chunk, int keep_first, float scale, float softcap, const float* sink,
+                                        int dtype, int* error, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (num_heads < 1 || num_kv_heads < 1 || num_heads % num_kv_heads != 0 || head_dim < 1 ||
       keep_first < 0 || head_dim > kMaxHeadDim || value_dim < 1 || value_dim > kMaxHeadDim || page_size < 1 || table_width < 1 ||
@@ -127,12 +129,12 @@ extern "C" int distie_attention_generic(const void* q, int q_row_stride, void* o
     attention_generic_kernel<<<grid, threads, 0, stream>>>(
         (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, out_row_stride, positions, token_seq, seq_seat,
         block_table, table_width, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, group, num_kv_heads,
-        head_dim, value_dim, page_size, num_pages, window, chunk, keep_first, scale, error);
+        head_dim, value_dim, page_size, num_pages, window, chunk, keep_first, scale, softcap, sink, error);
   else if (dtype == DISTIE_F32)
     attention_generic_kernel<<<grid, threads, 0, stream>>>(
         (const float*)q, q_row_stride, (float*)out, out_row_stride, positions, token_seq, seq_seat, block_table,
         table_width, (const float*)k_cache, (const float*)v_cache, group, num_kv_heads, head_dim, value_dim, page_size,
-        num_pages, window, chunk, keep_first, scale, error);
+        num_pages, window, chunk, keep_first, scale, softcap, sink, error);
   else
     return DISTIE_ERR_UNSUPPORTED;
   DISTIE_LAUNCH_CHECK();

@@ -60,6 +60,25 @@ __host__ __device__ __forceinline__ int first_visible_key(int pos, int window, i
   return first;
 }
 
+// A cap on a score: cap * tanh(s / cap) with cap > 0; cap <= 0 leaves the score as it is.
+__device__ __forceinline__ float cap_score(float s, float cap) { return cap > 0.f ? cap * tanhf(s / cap) : s; }
+// The same for kernels that serve in 16 bits: tanh(x) = 1 - 2 / (exp(2x) + 1) on the fast exponential
+// (relative error of the order of 1e-6, exact limits at both ends).
+__device__ __forceinline__ float cap_score_fast(float s, float cap) {
+  if (cap <= 0.f) return s;
+  return cap * (1.f - __fdividef(2.f, __expf(2.f * s / cap) + 1.f));
+}
+
+// A sink in a softmax: one more term exp(sink) in the denominator that has no value.  Given the running maximum `m`
+// and sum `l` over the keys (sum of exp(s - m)), returns the factor the mix (sum of exp(s - m) v) is multiplied by:
+// 1 / (l + exp(sink - m)), evaluated around the larger of m and sink so that neither exponential overflows.
+__device__ __forceinline__ float sink_inverse(float m, float l, float sink) {
+  const float top = fmaxf(m, sink);
+  const float keys = m == -INFINITY ? 0.f : expf(m - top);
+  const float total = l * keys + expf(sink - top);
+  return total > 0.f ? keys / total : 0.f;
+}
+
 // Sum over a block of up to 1024 threads; `scratch` holds 32 floats of shared memory.
 // Every thread gets the result.  Safe to call repeatedly with the same scratch.
 __device__ __forceinline__ float block_sum(float v, float* scratch) {

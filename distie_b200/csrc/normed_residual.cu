@@ -202,6 +202,92 @@ qk_rope_norm_write_kernel(SlicedRows qk, const float* __restrict__ bias, T* __re
   }
 }
 
+// From the float32 projection [q | k | v] (a matrix or the slices of a split product; columns behind these are not
+// read) to q in its buffer and k and v in their pages.  A block per token, a warp per head in turns.  For q and k
+// heads, in this order: bias; with `normed` the division by the head's root mean square (eps inside the root) and,
+// where a weight is given, the multiplication by it (head_dim floats shared by the heads); the rotation of the
+// first rotary_dim elements; for q the temperature 1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1)
+// (temp_every > 0).  v heads (value_dim elements, which may differ from head_dim) get their bias and are stored.
+template <typename T>
+__global__ void __launch_bounds__(kRopeWarps * 32)
+qkv_norm_write_kernel(SlicedRows qkv, const float* __restrict__ bias, T* __restrict__ q_out, int q_out_stride,
+                      const int* __restrict__ positions, const int* __restrict__ token_seq,
+                      const int* __restrict__ seq_seat, const int* __restrict__ block_table, int table_width,
+                      const float* __restrict__ inv_freq, float factor, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                      int num_heads, int num_kv_heads, int head_dim, int value_dim, int rotary_dim, int interleaved,
+                      int page_size, int num_pages, int write, int normed, float norm_eps,
+                      const float* __restrict__ q_weight, const float* __restrict__ k_weight, float temp_coef,
+                      int temp_every, int* __restrict__ error) {
+  extern __shared__ __align__(16) float heads_s[];  // kRopeWarps pieces of `piece` floats, then cos and sin of the token
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int piece = max(head_dim, value_dim);
+  float* head_s = heads_s + (size_t)warp * piece;
+  const int pos = positions[t];
+  const int half = rotary_dim / 2;
+  float* cos_s = heads_s + (size_t)kRopeWarps * piece;  // the token's angles serve all of its heads
+  float* sin_s = cos_s + half;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    float sn, cs;
+    sincosf((float)pos * inv_freq[i], &sn, &cs);
+    cos_s[i] = cs * factor;
+    sin_s[i] = sn * factor;
+  }
+  __syncthreads();
+  int page = -1;
+  if (write) {
+    const int seat = seq_seat[token_seq[t]];
+    const int column = pos / page_size;
+    page = column < table_width ? block_table[(size_t)seat * table_width + column] : -1;
+    if (page < 0 || page >= num_pages) {
+      if (threadIdx.x == 0 && error) atomicExch(error, 2);
+      page = -1;
+    }
+  }
+  const float temperature = temp_every > 0 ? 1.f + temp_coef * logf((float)((pos + 1) / temp_every) + 1.f) : 1.f;
+  const int k_column0 = num_heads * head_dim, v_column0 = (num_heads + num_kv_heads) * head_dim;
+  const int heads_here = num_heads + (write ? 2 * num_kv_heads : 0);
+  for (int head = blockIdx.y * kRopeWarps + warp; head < heads_here; head += gridDim.y * kRopeWarps) {
+    const bool is_query = head < num_heads, is_value = head >= num_heads + num_kv_heads;
+    if (is_value) {
+      if (page < 0) continue;
+      const int kv_head = head - num_heads - num_kv_heads;
+      const int column0 = v_column0 + kv_head * value_dim;
+      T* dst = v_cache + (((size_t)page * num_kv_heads + kv_head) * page_size + pos % page_size) * value_dim;
+      for (int e = lane; e < value_dim; e += 32)
+        dst[e] = from_float<T>(qkv.at(t, column0 + e) + (bias ? bias[column0 + e] : 0.f));
+      continue;
+    }
+    const int column0 = is_query ? head * head_dim : k_column0 + (head - num_heads) * head_dim;
+    float ss = 0.f;
+    for (int e = lane; e < head_dim; e += 32) {
+      const float value = qkv.at(t, column0 + e) + (bias ? bias[column0 + e] : 0.f);
+      head_s[e] = value;
+      ss += value * value;
+    }
+    const float unit = normed ? rsqrtf(warp_sum(ss) / (float)head_dim + norm_eps) : 1.f;
+    const float* weight = is_query ? q_weight : k_weight;
+    __syncwarp();
+    if (normed)
+      for (int e = lane; e < head_dim; e += 32) head_s[e] = head_s[e] * unit * (weight ? weight[e] : 1.f);
+    __syncwarp();
+    for (int i = lane; i < half; i += 32) {  // every pair is read and written by one lane
+      const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + half;
+      const float sn = sin_s[i], cs = cos_s[i];
+      const float u = head_s[a], v = head_s[b];
+      head_s[a] = u * cs - v * sn;
+      head_s[b] = v * cs + u * sn;
+    }
+    __syncwarp();
+    if (is_query || page >= 0) {
+      T* dst = is_query ? q_out + (size_t)t * q_out_stride + column0
+                        : k_cache + (((size_t)page * num_kv_heads + (head - num_heads)) * page_size + pos % page_size) * head_dim;
+      const float times = is_query ? temperature : 1.f;
+      for (int e = lane; e < head_dim; e += 32) dst[e] = from_float<T>(head_s[e] * times);
+    }
+    __syncwarp();  // before the next head overwrites the piece
+  }
+}
+
 }  // namespace distie
 
 using namespace distie;
@@ -288,6 +374,46 @@ extern "C" int distie_qk_rope_norm_write(const float* qk, int qk_stride, int spl
         rows, bias, (float*)q_out, q_out_stride, positions, token_seq, seq_seat, block_table, table_width, inv_freq,
         factor, (float*)k_cache, (float*)v_cache, num_heads, num_kv_heads, head_dim, rotary_dim, interleaved, page_size,
         num_pages, write, normed, norm_eps, error);
+  else
+    return DISTIE_ERR_UNSUPPORTED;
+  DISTIE_LAUNCH_CHECK();
+  return 0;
+}
+
+// qkv: float32 [tokens, heads * head_dim + kv_heads * (head_dim + value_dim) (+ columns that are not read)] with row
+// stride `qkv_stride`, or `splits` such matrices `split_stride` floats apart whose sum it is.  write == 0: only q is
+// made.  normed == 0: no norm; q_weight / k_weight null: no weight.  temp_every <= 0: no temperature.
+extern "C" int distie_qkv_norm_write(const float* qkv, int qkv_stride, int splits, long long split_stride, const float* bias,
+                                     void* q_out, int q_out_stride, const int* positions, const int* token_seq,
+                                     const int* seq_seat, const int* block_table, int table_width, const float* inv_freq,
+                                     float factor, void* k_cache, void* v_cache, int tokens, int num_heads, int num_kv_heads,
+                                     int head_dim, int value_dim, int rotary_dim, int interleaved, int page_size,
+                                     int num_pages, int write, int normed, float norm_eps, const float* q_weight,
+                                     const float* k_weight, float temp_coef, int temp_every, int dtype, int* error,
+                                     cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (num_heads < 1 || num_kv_heads < 1 || head_dim < 1 || head_dim > 1024 || value_dim < 1 || value_dim > 1024 ||
+      rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1) || (rotary_dim > 0 && inv_freq == nullptr) || splits < 1 ||
+      page_size < 1 || num_heads + 2 * num_kv_heads > 65535 || (write && (k_cache == nullptr || v_cache == nullptr)))
+    return DISTIE_ERR_ARG;
+  const int heads_all = num_heads + 2 * num_kv_heads;
+  // Few tokens: the heads of a token spread over several blocks, so that the step fills more of the machine.
+  const dim3 grid(tokens, tokens < 512 ? (heads_all + kRopeWarps - 1) / kRopeWarps : 1);
+  const int threads = kRopeWarps * 32;
+  const int piece = head_dim > value_dim ? head_dim : value_dim;
+  const size_t shared = ((size_t)kRopeWarps * piece + rotary_dim) * sizeof(float);
+  const SlicedRows rows{qkv, qkv_stride, splits, split_stride};
+  if (dtype == DISTIE_BF16)
+    qkv_norm_write_kernel<<<grid, threads, shared, stream>>>(
+        rows, bias, (__nv_bfloat16*)q_out, q_out_stride, positions, token_seq, seq_seat, block_table, table_width,
+        inv_freq, factor, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, num_heads, num_kv_heads, head_dim, value_dim,
+        rotary_dim, interleaved, page_size, num_pages, write, normed, norm_eps, q_weight, k_weight, temp_coef, temp_every,
+        error);
+  else if (dtype == DISTIE_F32)
+    qkv_norm_write_kernel<<<grid, threads, shared, stream>>>(
+        rows, bias, (float*)q_out, q_out_stride, positions, token_seq, seq_seat, block_table, table_width, inv_freq,
+        factor, (float*)k_cache, (float*)v_cache, num_heads, num_kv_heads, head_dim, value_dim, rotary_dim, interleaved,
+        page_size, num_pages, write, normed, norm_eps, q_weight, k_weight, temp_coef, temp_every, error);
   else
     return DISTIE_ERR_UNSUPPORTED;
   DISTIE_LAUNCH_CHECK();

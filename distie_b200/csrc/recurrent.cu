@@ -30,11 +30,12 @@ struct Sliced {
   int stride;  // of a row
   int splits;
   long long split_stride;
+  const float* bias = nullptr;  // per column, added to the sum of the slices (a projection's bias); null: none
   __device__ __forceinline__ float at(size_t row, int col) const {
     const float* q = p + row * stride + col;
     float v = q[0];
     for (int s = 1; s < splits; ++s) v += q[(size_t)s * split_stride];
-    return v;
+    return bias ? v + bias[col] : v;
   }
   __device__ __forceinline__ float4 at4(size_t row, int col) const {
     const float* q = p + row * stride + col;
@@ -42,6 +43,10 @@ struct Sliced {
     for (int s = 1; s < splits; ++s) {
       const float4 w = *reinterpret_cast<const float4*>(q + (size_t)s * split_stride);
       v.x += w.x; v.y += w.y; v.z += w.z; v.w += w.w;
+    }
+    if (bias) {
+      const float4 b = *reinterpret_cast<const float4*>(bias + col);
+      v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
     }
     return v;
   }
@@ -199,6 +204,19 @@ __global__ void head_gate_vec_kernel(T* __restrict__ x, Sliced logits, int num_h
     const float s = sigmoid_f(logits.at(t, h));
     float4 v = load4(x + e);
     v.x *= s; v.y *= s; v.z *= s; v.w *= s;
+    store4(x + e, v);
+  }
+}
+
+// The gate element by element (a "head" of one element each): four columns a thread, their four logits in one load.
+template <typename T>
+__global__ void element_gate_vec_kernel(T* __restrict__ x, Sliced logits, int columns, size_t quads) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < quads; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t e = i * 4;
+    const size_t t = e / (size_t)columns;
+    const float4 g = logits.at4(t, (int)(e % (size_t)columns));
+    float4 v = load4(x + e);
+    v.x *= sigmoid_f(g.x); v.y *= sigmoid_f(g.y); v.z *= sigmoid_f(g.z); v.w *= sigmoid_f(g.w);
     store4(x + e, v);
   }
 }
@@ -982,6 +1000,17 @@ extern "C" int distie_head_gate(void* x, const float* logits_ptr, int logit_stri
   const Sliced logits{logits_ptr, logit_stride, splits, split_stride};
   const size_t total = (size_t)tokens * num_heads * dim;
   const int threads = 256;
+  if (dim == 1 && num_heads % 4 == 0 && logit_stride % 4 == 0 && (splits == 1 || split_stride % 4 == 0) &&
+      (((uintptr_t)x | (uintptr_t)logits_ptr) & 15) == 0 && (dtype == DISTIE_BF16 || dtype == DISTIE_F32)) {
+    const size_t quads = total / 4, want_vec = (quads + threads - 1) / threads;
+    const int blocks_vec = (int)(want_vec < 148 * 32 ? want_vec : 148 * 32);
+    if (dtype == DISTIE_BF16)
+      element_gate_vec_kernel<<<blocks_vec, threads, 0, stream>>>((__nv_bfloat16*)x, logits, num_heads, quads);
+    else
+      element_gate_vec_kernel<<<blocks_vec, threads, 0, stream>>>((float*)x, logits, num_heads, quads);
+    DISTIE_LAUNCH_CHECK();
+    return 0;
+  }
   if (dim % 4 == 0 && ((uintptr_t)x & 15) == 0 && (dtype == DISTIE_BF16 || dtype == DISTIE_F32)) {
     const size_t quads = total / 4, want_vec = (quads + threads - 1) / threads;
     const int blocks_vec = (int)(want_vec < 148 * 32 ? want_vec : 148 * 32);
@@ -1018,16 +1047,16 @@ extern "C" int distie_short_conv(const float* x_ptr, int x_stride, int splits, l
                                  const float* weight, const float* bias, float* state,
                                  const int* token_seq, const int* token_first, const int* seq_bounds,
                                  const int* seq_seat, int tokens, int num_seqs, int channels, int taps, int silu,
-                                 int single, float* out, cudaStream_t stream) {
+                                 int single, float* out, const float* input_bias, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (channels < 1 || taps < 1 || num_seqs < 1) return DISTIE_ERR_ARG;
   if (taps > kMaxTaps) return DISTIE_ERR_UNSUPPORTED;
   if (taps > 1 && state == nullptr) return DISTIE_ERR_ARG;
   if (splits < 1) return DISTIE_ERR_ARG;
-  const Sliced x{x_ptr, x_stride, splits, split_stride};
+  const Sliced x{x_ptr, x_stride, splits, split_stride, input_bias};  // input_bias [channels]: added to every input of the step
   const int threads = 128;
   const bool vec = !single && channels % 4 == 0 && x_stride % 4 == 0 && split_stride % 4 == 0 &&
-                   (((uintptr_t)x_ptr | (uintptr_t)state | (uintptr_t)out | (uintptr_t)bias) & 15) == 0;
+                   (((uintptr_t)x_ptr | (uintptr_t)state | (uintptr_t)out | (uintptr_t)bias | (uintptr_t)input_bias) & 15) == 0;
   if (vec) {
     const dim3 grid((channels / 4 + threads - 1) / threads, tokens);
     if (taps == 4 && ((uintptr_t)weight & 15) == 0) {

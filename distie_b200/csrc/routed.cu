@@ -39,10 +39,13 @@ constexpr int kMaxTop = 32;
 // `count` floats.  With count > 1 and keep < count the experts form `count` equal groups of neighbours; a group's
 // score is the sum of its two largest scores (of its one score in groups of one) and only the experts of the `keep`
 // best groups (ties to the lower group) stay eligible.  Then the `top` largest eligible scores, ties to the lower
-// index; the weights are the scores times `weight_scale`.
+// index; the weights are the scores times `weight_scale`.  `plain` holds the scores the weights are taken from: `mine`
+// itself, or a second array when the choice runs on scores with a correction added (which may lie anywhere, so what
+// is taken or not eligible is marked with -infinity).  `normalise`: the chosen scores are divided by their sum + 1e-20.
 __device__ __forceinline__ void route_choose(float* mine, float* group_s, int experts, int top, int count, int keep,
                                              float weight_scale, int* __restrict__ ids, float* __restrict__ weights,
-                                             int lane) {
+                                             int lane, const float* plain = nullptr, int normalise = 0) {
+  if (plain == nullptr) plain = mine;
   if (count > 1 && keep < count) {
     const int size = experts / count;
     for (int g = lane; g < count; g += 32) {
@@ -72,11 +75,12 @@ __device__ __forceinline__ void route_choose(float* mine, float* group_s, int ex
       __syncwarp();
     }
     for (int e = lane; e < experts; e += 32)
-      if (group_s[e / size] != -3.f) mine[e] = -2.f;
+      if (group_s[e / size] != -3.f) mine[e] = -INFINITY;
     __syncwarp();
   }
+  float total = 0.f;
   for (int j = 0; j < top; ++j) {
-    float best = -1.f;  // scores lie in [0, 1]; a score taken or not eligible is -2
+    float best = -INFINITY;  // a score taken or not eligible is -infinity
     int at = experts;
     for (int e = lane; e < experts; e += 32) {
       const float sc = mine[e];
@@ -88,13 +92,47 @@ __device__ __forceinline__ void route_choose(float* mine, float* group_s, int ex
       const int other_at = __shfl_xor_sync(0xffffffffu, at, offset);
       if (other > best || (other == best && other_at < at)) { best = other; at = other_at; }
     }
-    if (lane == 0) {
+    if (lane == 0 && at < experts) {
       ids[j] = at;
-      weights[j] = best * weight_scale;
-      mine[at] = -2.f;
+      weights[j] = plain[at] * weight_scale;
+      total += plain[at];
+      mine[at] = -INFINITY;
     }
     __syncwarp();
   }
+  if (normalise && lane == 0) {
+    const float inv = 1.f / (total + 1e-20f);
+    for (int j = 0; j < top; ++j) weights[j] *= inv;
+  }
+}
+
+// What a warp does to a token's row of logits before it chooses: with `softmax` the scores become the softmax over
+// the row (else the row already holds sigmoid scores); with a `correction` the plain scores are kept in `plain_s` and
+// the row itself becomes score + correction.  Returns where the plain scores lie.
+__device__ __forceinline__ const float* route_scores(float* mine, float* plain_s, int experts, int softmax,
+                                                     const float* __restrict__ correction, int lane) {
+  if (softmax) {
+    float top = -INFINITY;
+    for (int e = lane; e < experts; e += 32) top = fmaxf(top, mine[e]);
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, offset));
+    float sum = 0.f;
+    for (int e = lane; e < experts; e += 32) {
+      const float ex = expf(mine[e] - top);
+      mine[e] = ex;
+      sum += ex;
+    }
+    sum = warp_sum(sum);
+    for (int e = lane; e < experts; e += 32) mine[e] = mine[e] / sum;
+    __syncwarp();
+  }
+  if (correction == nullptr) return mine;
+  for (int e = lane; e < experts; e += 32) {
+    plain_s[e] = mine[e];
+    mine[e] += correction[e];
+  }
+  __syncwarp();
+  return plain_s;
 }
 
 // TOK tokens a block: their rows wait in shared memory as floats and a warp takes an expert at a time for all of
@@ -104,11 +142,12 @@ template <typename T, int TOK, int VEC>
 __global__ void __launch_bounds__(kRouteThreads)
 route_top_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ router, int tokens, int hidden, int experts,
                  int top, int* __restrict__ ids, float* __restrict__ weights, int group_count, int group_keep,
-                 float weight_scale, int extra, float* __restrict__ extra_out) {
+                 float weight_scale, int extra, float* __restrict__ extra_out, int softmax,
+                 const float* __restrict__ correction, int normalise) {
   extern __shared__ __align__(16) float route_s[];
   float* x_s = route_s;
-  float* scores_s = route_s + (size_t)TOK * hidden;  // per token: experts scores, then group_count floats
-  const int score_row = experts + group_count;
+  float* scores_s = route_s + (size_t)TOK * hidden;  // per token: experts scores, group_count floats, experts plain scores
+  const int score_row = 2 * experts + group_count;
   const int t0 = blockIdx.x * TOK, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int live = min(TOK, tokens - t0);
   for (int r = 0; r < TOK; ++r) {
@@ -155,7 +194,7 @@ route_top_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ ro
     for (int r = 0; r < TOK; ++r) {
       const float z = warp_sum(dot[r]);
       if (lane == 0) {
-        if (e < experts) scores_s[r * score_row + e] = routed_sigmoid(z);
+        if (e < experts) scores_s[r * score_row + e] = softmax ? z : routed_sigmoid(z);
         else if (r < live) extra_out[(size_t)(t0 + r) * extra + e - experts] = z;
       }
     }
@@ -164,23 +203,30 @@ route_top_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ ro
   for (int r = warp; r < live; r += kRouteThreads / 32) {
     float* mine = scores_s + (size_t)r * score_row;
     const size_t t = t0 + r;
-    route_choose(mine, mine + experts, experts, top, group_count, group_keep, weight_scale, ids + t * top, weights + t * top, lane);
+    const float* plain = route_scores(mine, mine + experts + group_count, experts, softmax, correction, lane);
+    route_choose(mine, mine + experts, experts, top, group_count, group_keep, weight_scale, ids + t * top, weights + t * top, lane,
+                 plain, normalise);
   }
 }
 
 // The choice alone, from float32 logits [tokens, experts] that a product left: a warp per token.
 __global__ void __launch_bounds__(kRouteThreads)
 route_pick_kernel(const float* __restrict__ logits, int logit_stride, int tokens, int experts, int top,
-                  int* __restrict__ ids, float* __restrict__ weights, int group_count, int group_keep, float weight_scale) {
-  extern __shared__ float pick_s[];  // per warp: a row of scores, then group_count floats
+                  int* __restrict__ ids, float* __restrict__ weights, int group_count, int group_keep, float weight_scale,
+                  int softmax, const float* __restrict__ correction, int normalise) {
+  extern __shared__ float pick_s[];  // per warp: a row of scores, group_count floats, a row of plain scores
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int t = blockIdx.x * (kRouteThreads / 32) + warp;
   if (t >= tokens) return;
-  float* mine = pick_s + (size_t)warp * (experts + group_count);
-  for (int e = lane; e < experts; e += 32) mine[e] = routed_sigmoid(logits[(size_t)t * logit_stride + e]);
+  float* mine = pick_s + (size_t)warp * (2 * experts + group_count);
+  for (int e = lane; e < experts; e += 32) {
+    const float z = logits[(size_t)t * logit_stride + e];
+    mine[e] = softmax ? z : routed_sigmoid(z);
+  }
   __syncwarp();
+  const float* plain = route_scores(mine, mine + experts + group_count, experts, softmax, correction, lane);
   route_choose(mine, mine + experts, experts, top, group_count, group_keep, weight_scale, ids + (size_t)t * top,
-               weights + (size_t)t * top, lane);
+               weights + (size_t)t * top, lane, plain, normalise);
 }
 
 // plan layout (int32): [0] number of tiles; [1 .. 1 + experts] offsets of the experts' slots; then
@@ -214,7 +260,7 @@ __host__ __device__ inline RoutePlan plan_views(int* base, int pairs, int expert
 // counts_s: 2 * experts ints of dynamic shared memory (counts, then cursors).
 __global__ void __launch_bounds__(1024)
 route_plan_kernel(const int* __restrict__ ids, const float* __restrict__ weights, int tokens, int top, int experts,
-                  int tile, int* __restrict__ plan_base, int* __restrict__ error) {
+                  int tile, int* __restrict__ plan_base, int* __restrict__ error, int identity) {
   extern __shared__ int counts_s[];
   int* cursor_s = counts_s + experts;
   const int pairs = tokens * top;
@@ -223,7 +269,10 @@ route_plan_kernel(const int* __restrict__ ids, const float* __restrict__ weights
   __syncthreads();
   for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
     const int e = ids[p];
-    if (e < 0 || e >= experts) { if (error) atomicExch(error, 7); continue; }
+    if (e < 0 || e >= experts) {  // ids experts .. experts + identity - 1 return their input and are in no tile
+      if ((e < 0 || e >= experts + identity) && error) atomicExch(error, 7);
+      continue;
+    }
     atomicAdd(&counts_s[e], 1);
   }
   __syncthreads();
@@ -460,6 +509,7 @@ __global__ void routed_gather_kernel(const T* __restrict__ x, int x_stride, int*
                                      int experts, int tile, T* __restrict__ gathered, int hidden, int scale_in) {
   const RoutePlan plan = plan_views(plan_base, pairs, experts, tile);
   const int slot = blockIdx.x;
+  if (slot >= plan.offsets[experts]) return;  // fewer slots than pairs: some pairs go to no expert's product
   const T* src = x + (size_t)plan.source[slot] * x_stride;
   const float scale = scale_in ? plan.scale[slot] : 1.f;
   T* dst = gathered + (size_t)slot * hidden;
@@ -483,6 +533,7 @@ __global__ void routed_scatter_kernel(const float* __restrict__ y, int* __restri
                                       int tile, float* __restrict__ out, int hidden, int scale_out) {
   const RoutePlan plan = plan_views(plan_base, pairs, experts, tile);
   const int slot = blockIdx.x;
+  if (slot >= plan.offsets[experts]) return;
   const float scale = scale_out ? plan.scale[slot] : 1.f;
   const float* src = y + (size_t)slot * hidden;
   float* dst = out + (size_t)plan.dest[slot] * hidden;
@@ -494,6 +545,21 @@ __global__ void routed_scatter_kernel(const float* __restrict__ y, int* __restri
     return;
   }
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = src[c] * scale;
+}
+
+// Pairs whose id lies behind the experts' (experts .. experts + identity - 1) stand for an expert that returns its
+// input: out[choice, token, :] = weight * x[token, :].  A block per pair; pairs of real experts are left alone.
+template <typename T>
+__global__ void routed_identity_kernel(const T* __restrict__ x, int x_stride, const int* __restrict__ ids,
+                                       const float* __restrict__ weights, int tokens, int top, int experts,
+                                       float* __restrict__ out, int hidden) {
+  const int p = blockIdx.x;
+  if (ids[p] < experts) return;
+  const int token = p / top, choice = p % top;
+  const float w = weights[p];
+  const T* src = x + (size_t)token * x_stride;
+  float* dst = out + ((size_t)choice * tokens + token) * hidden;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = w * to_float(src[c]);
 }
 
 // ---- grouped products of steps with few rows per expert: every weight row is streamed once per tile of eight rows -------
@@ -630,8 +696,10 @@ using namespace distie;
 // x [tokens, hidden] and router [experts, hidden] of one type; ids, weights [tokens, top].
 extern "C" int distie_route_top(const void* x, int x_stride, const void* router, int tokens, int hidden, int experts,
                                 int top, int* ids, float* weights, int group_count, int group_keep, float weight_scale,
-                                int extra, float* extra_out, int dtype, cudaStream_t stream) {
+                                int extra, float* extra_out, int softmax, const float* correction, int normalise,
+                                int dtype, cudaStream_t stream) {
   if (tokens <= 0) return 0;
+  if (correction != nullptr && group_count > 1 && group_keep < group_count) return DISTIE_ERR_ARG;
   if (hidden < 1 || experts < 1 || top < 1 || top > experts || top > kMaxTop || experts > 8192 || group_count < 1 ||
       experts % group_count != 0 || group_keep < 1 || group_keep > group_count || extra < 0 || (extra > 0 && !extra_out) ||
       top > group_keep * (experts / group_count))
@@ -639,14 +707,14 @@ extern "C" int distie_route_top(const void* x, int x_stride, const void* router,
   if (dtype != DISTIE_BF16 && dtype != DISTIE_F32) return DISTIE_ERR_UNSUPPORTED;
   const int wide = dtype == DISTIE_BF16 ? 8 : 4;
   const bool vec = hidden % wide == 0 && ((uintptr_t)router & 15) == 0;
-  const int tok = tokens >= 64 && (size_t)4 * (hidden + experts + group_count) * sizeof(float) <= 96 * 1024 ? 4 : 1;
-  const size_t shared = (size_t)tok * (hidden + experts + group_count) * sizeof(float);
+  const int tok = tokens >= 64 && (size_t)4 * (hidden + 2 * experts + group_count) * sizeof(float) <= 96 * 1024 ? 4 : 1;
+  const size_t shared = (size_t)tok * (hidden + 2 * experts + group_count) * sizeof(float);
   if (shared > 200 * 1024) return DISTIE_ERR_UNSUPPORTED;
   const unsigned blocks = (unsigned)((tokens + tok - 1) / tok);
   auto run = [&](auto kernel, auto xp, auto rp) {
     if (shared > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
     kernel<<<blocks, kRouteThreads, shared, stream>>>(xp, x_stride, rp, tokens, hidden, experts, top, ids, weights, group_count,
-                                                      group_keep, weight_scale, extra, extra_out);
+                                                      group_keep, weight_scale, extra, extra_out, softmax, correction, normalise);
   };
 #define DISTIE_ROUTE(T, VECV)                                                                             \
   do {                                                                                                    \
@@ -674,14 +742,35 @@ extern "C" long long distie_route_plan_words(int pairs, int experts, int tile) {
   return 1 + (experts + 1) + 3 * max_tiles + 3LL * pairs;
 }
 
+// Rows of `out` [top, tokens, hidden] of the pairs whose id is experts or more: weight * x[token] (see
+// routed_identity_kernel).
+extern "C" int distie_routed_identity(const void* x, int x_stride, const int* ids, const float* weights, int tokens, int top,
+                                      int experts, float* out, int hidden, int dtype, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  const int threads = hidden >= 1024 ? 256 : 128;
+  if (dtype == DISTIE_BF16)
+    routed_identity_kernel<<<tokens * top, threads, 0, stream>>>((const __nv_bfloat16*)x, x_stride, ids, weights, tokens, top,
+                                                                experts, out, hidden);
+  else if (dtype == DISTIE_F32)
+    routed_identity_kernel<<<tokens * top, threads, 0, stream>>>((const float*)x, x_stride, ids, weights, tokens, top, experts,
+                                                                out, hidden);
+  else
+    return DISTIE_ERR_UNSUPPORTED;
+  DISTIE_LAUNCH_CHECK();
+  return 0;
+}
+
 // x [tokens, hidden]; gate_up [experts, 2 ff, hidden]; down [experts, hidden, ff]; ids, weights [tokens, top];
+// ids experts .. experts + identity - 1 stand for experts that return their input (weight on the output only).
 // plan: distie_route_plan_words int32; mid [tokens * top, ff] of the type; out [top, tokens, hidden] float32.
 // weight_on_input: the pair's weight multiplies the expert's input, else its output.
 extern "C" int distie_routed_swiglu(const void* x, int x_stride, const int* ids, const float* weights, const void* gate_up,
                                     const void* down, int* plan, void* mid, float* out, int tokens, int top, int experts,
-                                    int hidden, int ff, int weight_on_input, float limit, int dtype, int* error, cudaStream_t stream) {
+                                    int hidden, int ff, int weight_on_input, float limit, int identity, int dtype, int* error,
+                                    cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (top < 1 || experts < 1 || hidden < 1 || ff < 1 || experts > 4096) return DISTIE_ERR_ARG;
+  if (top < 1 || experts < 1 || hidden < 1 || ff < 1 || experts > 4096 || identity < 0 || (identity > 0 && weight_on_input))
+    return DISTIE_ERR_ARG;
   if (dtype != DISTIE_BF16 && dtype != DISTIE_F32) return DISTIE_ERR_UNSUPPORTED;
   const int pairs = tokens * top;
   const int tile = distie_routed_tile(dtype, hidden, ff, pairs, experts);
@@ -689,8 +778,12 @@ extern "C" int distie_routed_swiglu(const void* x, int x_stride, const int* ids,
                    (((uintptr_t)x | (uintptr_t)gate_up | (uintptr_t)down | (uintptr_t)mid) & 15) == 0;
   if (tile == kMmaM && !mma) return DISTIE_ERR_UNSUPPORTED;
   route_plan_kernel<<<1, 1024, 2 * (size_t)experts * sizeof(int), stream>>>(ids, weights, tokens, top, experts, tile, plan,
-                                                                           error);
+                                                                           error, identity);
   DISTIE_LAUNCH_CHECK();
+  if (identity > 0) {
+    const int status = distie_routed_identity(x, x_stride, ids, weights, tokens, top, experts, out, hidden, dtype, stream);
+    if (status != 0) return status;
+  }
   const unsigned max_tiles = (unsigned)((pairs + tile - 1) / tile + experts);
   const int in = weight_on_input ? 1 : 0;
   if (tile == kRowsR) {
@@ -743,11 +836,11 @@ extern "C" int distie_routed_swiglu(const void* x, int x_stride, const int* ids,
 
 // The plan alone (see route_plan_kernel), for callers that run the grouped products themselves; `tile` rows a tile.
 extern "C" int distie_route_plan(const int* ids, const float* weights, int tokens, int top, int experts, int tile,
-                                 int* plan, int* error, cudaStream_t stream) {
+                                 int* plan, int* error, int identity, cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (top < 1 || experts < 1 || experts > 4096 || tile < 1) return DISTIE_ERR_ARG;
+  if (top < 1 || experts < 1 || experts > 4096 || tile < 1 || identity < 0) return DISTIE_ERR_ARG;
   route_plan_kernel<<<1, 1024, 2 * (size_t)experts * sizeof(int), stream>>>(ids, weights, tokens, top, experts, tile, plan,
-                                                                           error);
+                                                                           error, identity);
   DISTIE_LAUNCH_CHECK();
   return 0;
 }
@@ -777,17 +870,19 @@ extern "C" int distie_routed_scatter(const float* y, int* plan, int pairs, int e
 
 // ids and weights from float32 logits [tokens, experts] (row stride logit_stride): see route_pick_kernel.
 extern "C" int distie_route_pick(const float* logits, int logit_stride, int tokens, int experts, int top, int* ids,
-                                 float* weights, int group_count, int group_keep, float weight_scale, cudaStream_t stream) {
+                                 float* weights, int group_count, int group_keep, float weight_scale, int softmax,
+                                 const float* correction, int normalise, cudaStream_t stream) {
   if (tokens <= 0) return 0;
+  if (correction != nullptr && group_count > 1 && group_keep < group_count) return DISTIE_ERR_ARG;
   if (experts < 1 || top < 1 || top > experts || top > kMaxTop || experts > 4096 || group_count < 1 ||
       experts % group_count != 0 || group_keep < 1 || group_keep > group_count || top > group_keep * (experts / group_count))
     return DISTIE_ERR_ARG;
   const int warps = kRouteThreads / 32;
-  const size_t shared = (size_t)warps * (experts + group_count) * sizeof(float);
+  const size_t shared = (size_t)warps * (2 * experts + group_count) * sizeof(float);
   if (shared > 48 * 1024) cudaFuncSetAttribute(route_pick_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
   route_pick_kernel<<<(tokens + warps - 1) / warps, kRouteThreads, shared, stream>>>(logits, logit_stride, tokens, experts,
                                                                                     top, ids, weights, group_count, group_keep,
-                                                                                    weight_scale);
+                                                                                    weight_scale, softmax, correction, normalise);
   DISTIE_LAUNCH_CHECK();
   return 0;
 }

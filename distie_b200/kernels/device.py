@@ -387,17 +387,22 @@ class DeviceKernels(KernelSet):
         self._ran("attention_decode_mma_qkv", 0)
 
     def attention(self, qkv, out, step, kv, num_heads, num_kv_heads, head_dim, window, scale, chunk=None,
-                  keep_first=0) -> None:
+                  keep_first=0, softcap=0.0, sink=None) -> None:
         window = int(window) if window else 0
         chunk = int(chunk) if chunk else 0
         keep_first = int(keep_first) if keep_first and window else 0
+        softcap = float(softcap or 0.0)
+        sink_ptr = sink.data_ptr() if sink is not None else None
+        if sink is not None and (sink.dtype != torch.float32 or sink.numel() != num_heads or not sink.is_contiguous()):
+            raise KernelError("attention: the sink is one float32 per head")
+        extras = softcap > 0.0 or sink is not None  # served by the kernels on the FMA pipe
         value_dim = kv.v.shape[-1]
         same = value_dim == head_dim  # every kernel but the size-agnostic one wants values as large as keys
         n_dec = step.num_decode_tokens if head_dim in _DECODE_HEAD_DIMS and same else 0
         element = qkv.element_size()
         if n_dec > 0:
             splits = self.plan_splits(n_dec, num_heads, num_kv_heads, step.max_kv_len)
-            tensor_cores = self.dtype == torch.bfloat16 and head_dim in _PREFILL_HEAD_DIMS
+            tensor_cores = self.dtype == torch.bfloat16 and head_dim in _PREFILL_HEAD_DIMS and not extras
             if tensor_cores and splits <= 2 * _CLUSTER_SPLITS:
                 splits = min(splits, _CLUSTER_SPLITS)  # merged inside the kernel, by a cluster of CTAs
             in_kernel_merge = splits == 1 or (tensor_cores and splits <= _CLUSTER_SPLITS)
@@ -420,14 +425,14 @@ class DeviceKernels(KernelSet):
                 )
             else:
                 check(
-                    function("distie_attention_decode")(*head, keep_first, float(scale), splits, self.code,
+                    function("distie_attention_decode")(*head, keep_first, float(scale), softcap, sink_ptr, splits, self.code,
                                                         self.error_flag.data_ptr(), self._stream()),
                     "attention_decode",
                 )
             self._ran("attention_decode_mma" if tensor_cores else "attention_decode", 1 if in_kernel_merge else 2)
         rest = step.num_tokens - n_dec
         tiled = (rest > 0 and self.dtype == torch.bfloat16 and head_dim in _PREFILL_HEAD_DIMS and step.num_q_tiles
-                 and n_dec == step.num_decode_tokens and same)
+                 and n_dec == step.num_decode_tokens and same and not extras)
         if tiled and self._attention_tcgen05(qkv, out, step, kv, num_heads, num_kv_heads, head_dim, window, chunk, scale,
                                              keep_first):
             pass
@@ -451,8 +456,8 @@ class DeviceKernels(KernelSet):
                     step.positions.data_ptr() + 4 * n_dec, step.token_seq.data_ptr() + 4 * n_dec,
                     step.seq_seat.data_ptr(), kv.block_table.data_ptr(), kv.block_table.shape[-1],
                     kv.k.data_ptr(), kv.v.data_ptr(), rest, num_heads, num_kv_heads, head_dim, value_dim, kv.page_size,
-                    kv.num_pages, window, chunk, keep_first, float(scale), self.code, self.error_flag.data_ptr(),
-                    self._stream(),
+                    kv.num_pages, window, chunk, keep_first, float(scale), softcap, sink_ptr, self.code,
+                    self.error_flag.data_ptr(), self._stream(),
                 ),
                 "attention_generic",
             )
@@ -553,7 +558,7 @@ class DeviceKernels(KernelSet):
             made = step.derived["seq_index"] = (token_first, bounds)
         return made
 
-    def short_conv(self, x, weight, bias, state, step, activation="silu"):
+    def short_conv(self, x, weight, bias, state, step, activation="silu", input_bias=None):
         sliced = self._sliced(x, "short_conv")
         channels, taps = weight.shape
         out = torch.empty((step.num_tokens, channels), dtype=torch.float32, device=x.device)
@@ -564,7 +569,7 @@ class DeviceKernels(KernelSet):
                 *sliced, weight.data_ptr(), bias.data_ptr() if bias is not None else None,
                 state.data_ptr() if state is not None else None, step.token_seq.data_ptr(), token_first.data_ptr(),
                 seq_bounds.data_ptr(), step.seq_seat.data_ptr(), step.num_tokens, step.num_seqs, channels, taps, int(activation == "silu"), int(single), out.data_ptr(),
-                self._stream(),
+                input_bias.data_ptr() if input_bias is not None else None, self._stream(),
             ),
             "short_conv",
         )
@@ -655,6 +660,31 @@ class DeviceKernels(KernelSet):
         )
         self._ran("qk_rope_norm_write")
 
+    def qkv_norm_write(self, qkv, bias, step, kv, rotary, num_heads, num_kv_heads, head_dim, value_dim, norm_eps,
+                       q_weight, k_weight, q_temp, q_out) -> None:
+        write = kv is not None
+        if write and (kv.k.dtype != q_out.dtype or kv.v.shape[-1] != value_dim or kv.k.shape[-1] != head_dim):
+            raise KernelError("qkv_norm_write: the cache holds keys of head_dim and values of value_dim, of q's type")
+        table = kv.block_table if write else step.seq_seat
+        coef, every = (float(q_temp[0]), int(q_temp[1])) if q_temp else (0.0, 0)
+        check(
+            function("distie_qkv_norm_write")(
+                *self._sliced(qkv, "qkv_norm_write"), bias.data_ptr() if bias is not None else None, q_out.data_ptr(),
+                q_out.stride(0), step.positions.data_ptr(), step.token_seq.data_ptr(), step.seq_seat.data_ptr(),
+                table.data_ptr(), table.shape[-1] if write else 1,
+                rotary.inv_freq.data_ptr() if rotary is not None else None,
+                float(rotary.factor) if rotary is not None else 1.0, kv.k.data_ptr() if write else None,
+                kv.v.data_ptr() if write else None, step.num_tokens, num_heads, num_kv_heads, head_dim, value_dim,
+                rotary.rotary_dim if rotary is not None else 0, int(rotary.interleaved) if rotary is not None else 0,
+                kv.page_size if write else 1, kv.num_pages if write else 1, int(write), int(norm_eps is not None),
+                float(norm_eps or 0.0), q_weight.data_ptr() if q_weight is not None else None,
+                k_weight.data_ptr() if k_weight is not None else None, coef, every, _CODE[q_out.dtype],
+                self.error_flag.data_ptr(), self._stream(),
+            ),
+            "qkv_norm_write",
+        )
+        self._ran("qkv_norm_write")
+
     def activation(self, x, kind="silu", scale=1.0, scaled_columns=0):
         if kind not in ("silu", "none"):
             raise KernelError(f"activation {kind!r}: 'silu' or 'none'")
@@ -698,9 +728,12 @@ class DeviceKernels(KernelSet):
         self._ran("stabilized_readout")
         return out
 
-    def route_top(self, x, router, top, scoring="sigmoid", groups=None, weight_scale=1.0, extra_rows=0):
-        if scoring != "sigmoid":
-            raise KernelError(f"route_top: scoring {scoring!r} is not built; 'sigmoid' is")
+    def route_top(self, x, router, top, scoring="sigmoid", groups=None, weight_scale=1.0, extra_rows=0, correction=None,
+                  normalise=False):
+        if scoring not in ("sigmoid", "softmax"):
+            raise KernelError(f"route_top: scoring {scoring!r} is not built; 'sigmoid' and 'softmax' are")
+        softmax, norm = int(scoring == "softmax"), int(bool(normalise))
+        correction_ptr = correction.data_ptr() if correction is not None else None
         library.load_unit("routed")
         if x.dtype != router.dtype:
             x = x.to(router.dtype)  # a router kept in 32-bit reads the activations widened
@@ -717,7 +750,8 @@ class DeviceKernels(KernelSet):
             logits = torch.empty((tokens, experts + extra), dtype=torch.float32, device=x.device)
             self._gemm_tcgen05(x, router, logits, 1)
             check(function("distie_route_pick")(logits.data_ptr(), logits.stride(0), tokens, experts, top, ids.data_ptr(),
-                                                weights.data_ptr(), count, keep, float(weight_scale), self._stream()),
+                                                weights.data_ptr(), count, keep, float(weight_scale), softmax, correction_ptr,
+                                                norm, self._stream()),
                   "route_pick")
             self._ran("route_top")
             return (ids, weights, logits[:, experts:]) if extra else (ids, weights)
@@ -725,13 +759,17 @@ class DeviceKernels(KernelSet):
         check(
             function("distie_route_top")(x.data_ptr(), x.stride(0), router.data_ptr(), tokens, x.shape[1], experts, top,
                                          ids.data_ptr(), weights.data_ptr(), count, keep, float(weight_scale), extra,
-                                         extra_out.data_ptr() if extra else None, _CODE[x.dtype], self._stream()),
+                                         extra_out.data_ptr() if extra else None, softmax, correction_ptr, norm,
+                                         _CODE[x.dtype], self._stream()),
             "route_top",
         )
         self._ran("route_top")
         return (ids, weights, extra_out) if extra else (ids, weights)
 
-    def routed_swiglu(self, x, ids, weights, gate_up, down, scale_input=True, limit=None):
+    def routed_swiglu(self, x, ids, weights, gate_up, down, scale_input=True, limit=None, identity=0):
+        identity = int(identity or 0)
+        if identity and scale_input:
+            raise KernelError("routed_swiglu: experts that return their input go with the weight on the output")
         if gate_up.dtype != x.dtype or down.dtype != x.dtype:
             if gate_up.dtype != down.dtype:
                 raise KernelError("routed_swiglu: the experts' matrices are of one type")
@@ -745,7 +783,7 @@ class DeviceKernels(KernelSet):
             # rows that are no multiples of 16 bytes: the float32 form of the grouped products takes any size
             x, gate_up, down, code = x.float(), gate_up.float(), down.float(), 0
         if code == 1 and self.dtype == torch.bfloat16 and tokens * top >= _GROUPED_TENSOR_CORE_PAIRS:
-            return self._routed_swiglu_tcgen05(x, ids, weights, gate_up, down, scale_input, limit)
+            return self._routed_swiglu_tcgen05(x, ids, weights, gate_up, down, scale_input, limit, identity)
         tile = function("distie_routed_tile")(code, hidden, ff, tokens * top, experts)
         words = function("distie_route_plan_words")(tokens * top, experts, tile)
         plan = torch.empty(words, dtype=torch.int32, device=x.device)
@@ -755,14 +793,14 @@ class DeviceKernels(KernelSet):
             function("distie_routed_swiglu")(
                 x.data_ptr(), x.stride(0), ids.data_ptr(), weights.data_ptr(), gate_up.data_ptr(), down.data_ptr(),
                 plan.data_ptr(), mid.data_ptr(), out.data_ptr(), tokens, top, experts, hidden, ff, int(bool(scale_input)),
-                float(limit) if limit is not None else 0.0, code, self.error_flag.data_ptr(), self._stream(),
+                float(limit) if limit is not None else 0.0, identity, code, self.error_flag.data_ptr(), self._stream(),
             ),
             "routed_swiglu",
         )
         self._ran("routed_swiglu", 3)
         return out
 
-    def _routed_swiglu_tcgen05(self, x, ids, weights, gate_up, down, scale_input, limit=None):
+    def _routed_swiglu_tcgen05(self, x, ids, weights, gate_up, down, scale_input, limit=None, identity=0):
         """Prompt portions in bfloat16: the rows sorted by expert (and scaled by their weights) are gathered once, and
         both products run on the tcgen05 tile kernel over a list of row tiles that stays on the device."""
         tokens, top = ids.shape
@@ -774,8 +812,8 @@ class DeviceKernels(KernelSet):
         base = plan.data_ptr()
         tile_expert, tile_first, tile_rows = (base + 4 * (1 + experts + 1 + i * max_tiles) for i in range(3))
         stream, error = self._stream(), self.error_flag.data_ptr()
-        check(function("distie_route_plan")(ids.data_ptr(), weights.data_ptr(), tokens, top, experts, tile, base, error, stream),
-              "route_plan")
+        check(function("distie_route_plan")(ids.data_ptr(), weights.data_ptr(), tokens, top, experts, tile, base, error, identity,
+                                            stream), "route_plan")
         gathered = torch.empty((pairs, hidden), dtype=x.dtype, device=x.device)
         check(function("distie_routed_gather")(x.data_ptr(), x.stride(0), base, pairs, experts, tile, gathered.data_ptr(), hidden,
                                                int(bool(scale_input)), 1, stream), "routed_gather")
@@ -789,6 +827,9 @@ class DeviceKernels(KernelSet):
             mid.data_ptr(), ff, pairs, down.data_ptr(), experts, hidden, sorted_out.data_ptr(), hidden, hidden, ff, 1, 0.0, base,
             tile_expert, tile_first, tile_rows, max_tiles, self.sm_count, error, stream), "gemm_tcgen05_grouped")
         out = torch.empty((top, tokens, hidden), dtype=torch.float32, device=x.device)
+        if identity:
+            check(function("distie_routed_identity")(x.data_ptr(), x.stride(0), ids.data_ptr(), weights.data_ptr(), tokens, top,
+                                                     experts, out.data_ptr(), hidden, _CODE[x.dtype], stream), "routed_identity")
         check(function("distie_routed_scatter")(sorted_out.data_ptr(), base, pairs, experts, tile, out.data_ptr(), hidden,
                                                 int(not scale_input), stream), "routed_scatter")
         self._ran("routed_swiglu", 5)

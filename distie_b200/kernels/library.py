@@ -30,8 +30,11 @@ _SIGNATURES: dict[str, tuple[str, list]] = {
     ),
     "distie_rope_rows": ("base", [P, P, P, P, I, P, F, I, I, I, I, I, P, P, P, P]),
     "distie_bias_cast": ("base", [P, P, P, L, I, I, P]),
-    "distie_attention_generic": ("base", [P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P, P]),
-    "distie_attention_decode": ("base", [P, I, P, I, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, I, F, I, I, P, P]),
+    "distie_attention_generic": ("base", [P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, I, I, F, F, P, I, P, P]),
+    "distie_attention_decode": ("base", [P, I, P, I, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, I, F, F, P, I, I, P, P]),
+    "distie_qkv_norm_write": (
+        "base", [P, I, I, L, P, P, I, P, P, P, P, I, P, F, P, P, I, I, I, I, I, I, I, I, I, I, I, F, P, P, F, I, I, P, P]
+    ),
     "distie_norm_add_rmsnorm": ("base", [P, P, I, P, F, P, P, F, P, P, I, I, I, P]),
     "distie_qk_rope_norm_write": (
         "base", [P, I, I, L, P, P, I, P, P, P, P, I, P, F, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P, P]
@@ -53,22 +56,23 @@ _SIGNATURES: dict[str, tuple[str, list]] = {
     "distie_kv_write": ("state", [P, I, P, I, I, P, P, P, P, I, P, P, I, I, I, I, I, I, I, P, P]),
     "distie_head_gate": ("state", [P, P, I, I, L, I, I, I, I, P]),
     "distie_seq_index": ("state", [P, I, I, P, P, P]),
-    "distie_short_conv": ("state", [P, I, I, L, P, P, P, P, P, P, P, I, I, I, I, I, I, P, P]),
+    "distie_short_conv": ("state", [P, I, I, L, P, P, P, P, P, P, P, I, I, I, I, I, I, P, P, P]),
     "distie_linear_recurrence": (
         "state", [I, P, I, P, I, P, I, P, I, P, I, I, L, P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, P]
     ),
     "distie_activation": ("state", [P, I, I, L, P, I, I, I, F, I, P]),
     "distie_exp_gate_scan": ("state", [P, P, I, I, L, P, P, F, P, P, P, I, I, I, P, P, P, P]),
     "distie_stabilized_readout": ("state", [P, I, P, P, I, I, I, P]),
-    "distie_route_top": ("routed", [P, I, P, I, I, I, I, P, P, I, I, F, I, P, I, P]),
-    "distie_route_pick": ("routed", [P, I, I, I, I, P, P, I, I, F, P]),
+    "distie_route_top": ("routed", [P, I, P, I, I, I, I, P, P, I, I, F, I, P, I, P, I, I, P]),
+    "distie_route_pick": ("routed", [P, I, I, I, I, P, P, I, I, F, I, P, I, P]),
+    "distie_routed_identity": ("routed", [P, I, P, P, I, I, I, P, I, I, P]),
     "distie_routed_tile": ("routed", [I, I, I, I, I]),
     "distie_route_plan_words": ("routed", [I, I, I]),
-    "distie_route_plan": ("routed", [P, P, I, I, I, I, P, P, P]),
+    "distie_route_plan": ("routed", [P, P, I, I, I, I, P, P, I, P]),
     "distie_routed_gather": ("routed", [P, I, P, I, I, I, P, I, I, I, P]),
     "distie_routed_scatter": ("routed", [P, P, I, I, I, P, I, I, P]),
     "distie_gemm_tcgen05_grouped": ("bf16", [P, I, I, P, I, I, P, I, I, I, I, F, P, P, P, P, I, I, P, P]),
-    "distie_routed_swiglu": ("routed", [P, I, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P, P]),
+    "distie_routed_swiglu": ("routed", [P, I, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P, P]),
     "distie_latent_kv_write": (
         "latent", [P, I, I, L, I, P, I, P, I, F, P, I, P, P, P, P, I, P, F, I, I, P, I, I, I, I, I, P, P]
     ),
