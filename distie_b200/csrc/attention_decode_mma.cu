@@ -104,7 +104,7 @@ attention_decode_mma_kernel(const ProjectionInput proj,
                             const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
                             int num_heads, int group_size, int head_chunks, int num_kv_heads, int page_size,
                             int page_shift, int num_pages, int window, int key_chunk, int keep_first, float scale_log2, int cluster_merge,
-                            int* __restrict__ error) {
+                            const ScoreExtras extras, int* __restrict__ error) {
   constexpr int CPR = D / 8;                 // 16-byte chunks per row of keys or values
   constexpr int ROW_BYTES = D * 2;
   constexpr int TILE_BYTES = 16 * ROW_BYTES;  // 16 keys (or values)
@@ -427,10 +427,15 @@ attention_decode_mma_kernel(const ProjectionInput proj,
 #pragma unroll
     for (int nh = 0; nh < NH; ++nh) {
       float x[4];
-      x[0] = keep_lo ? st[nh][0] * scale_log2 : -INFINITY;
-      x[1] = keep_lo ? st[nh][1] * scale_log2 : -INFINITY;
-      x[2] = keep_hi ? st[nh][2] * scale_log2 : -INFINITY;
-      x[3] = keep_hi ? st[nh][3] * scale_log2 : -INFINITY;
+      if (extras.cap > 0.f) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) x[r] = capped_log2(st[nh][r], extras);
+      } else {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) x[r] = st[nh][r] * scale_log2;
+      }
+      if (!keep_lo) x[0] = x[1] = -INFINITY;
+      if (!keep_hi) x[2] = x[3] = -INFINITY;
 #pragma unroll
       for (int e = 0; e < 2; ++e) {  // column e of the lane: head 8 nh + 2c + e
         float m = fmaxf(x[e], x[e + 2]);
@@ -505,7 +510,8 @@ attention_decode_mma_kernel(const ProjectionInput proj,
     }
     const int head = head0 + hd;
     if (num_splits == 1) {
-      out[(size_t)t * out_row_stride + (size_t)head * D + e] = __float2bfloat16_rn(l_all > 0.f ? acc / l_all : 0.f);
+      const float inv = extras.sink ? sink_inverse_log2(m_all, l_all, extras.sink[head]) : (l_all > 0.f ? 1.f / l_all : 0.f);
+      out[(size_t)t * out_row_stride + (size_t)head * D + e] = __float2bfloat16_rn(acc * inv);
     } else if (cluster_merge) {
       cl_o[hd][e] = acc;
       if (e == 0) { cl_m[hd] = m_all; cl_l[hd] = l_all; }
@@ -547,7 +553,8 @@ attention_decode_mma_kernel(const ProjectionInput proj,
         l_all += ls[s] * weight;
         acc += os[s] * weight;
       }
-      out[(size_t)t * out_row_stride + (size_t)(head0 + hd) * D + e] = __float2bfloat16_rn(l_all > 0.f ? acc / l_all : 0.f);
+      const float inv = extras.sink ? sink_inverse_log2(m_all, l_all, extras.sink[head0 + hd]) : (l_all > 0.f ? 1.f / l_all : 0.f);
+      out[(size_t)t * out_row_stride + (size_t)(head0 + hd) * D + e] = __float2bfloat16_rn(acc * inv);
     }
     cluster_barrier_exit();  // no CTA leaves while another may still read its shared memory
   }
@@ -562,7 +569,7 @@ constexpr int kMergeThreads = 256;
 __global__ void __launch_bounds__(kMergeThreads)
 attention_decode_mma_merge_kernel(const float* __restrict__ scratch_o, const float* __restrict__ scratch_ml,
                                   __nv_bfloat16* __restrict__ out, int out_row_stride, int num_heads, int head_dim,
-                                  int num_splits) {
+                                  int num_splits, const float* __restrict__ sink) {
   __shared__ float sh_max[kMergeThreads / 32];
   __shared__ float sh_l[kMergeThreads / 16];
   __shared__ float4 sh_acc[kMergeThreads];
@@ -605,7 +612,7 @@ attention_decode_mma_merge_kernel(const float* __restrict__ scratch_o, const flo
       sum.x += part.x; sum.y += part.y; sum.z += part.z; sum.w += part.w;
       l_all += sh_l[r];
     }
-    const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+    const float inv = sink ? sink_inverse_log2(m_all, l_all, sink[head]) : (l_all > 0.f ? 1.f / l_all : 0.f);
     __nv_bfloat162 lo = __floats2bfloat162_rn(sum.x * inv, sum.y * inv), hi = __floats2bfloat162_rn(sum.z * inv, sum.w * inv);
     uint2 packed;
     packed.x = *reinterpret_cast<uint32_t*>(&lo);
@@ -634,7 +641,7 @@ static int launch_decode_mma(const ProjectionInput* proj, const void* q, int q_r
                              const int* block_table, int table_width, const void* k_cache, const void* v_cache,
                              int tokens, int num_heads, int num_kv_heads, int head_dim, int page_size, int num_pages,
                              int window, int key_chunk, int keep_first, float scale, int num_splits, int* error,
-                             cudaStream_t stream) {
+                             cudaStream_t stream, const ScoreExtras extras = ScoreExtras()) {
   if (tokens <= 0) return 0;
   if (keep_first < 0 || (proj && keep_first)) return DISTIE_ERR_ARG;
   if (num_heads < 1 || num_kv_heads < 1 || num_heads % num_kv_heads != 0 || page_size < 1 || table_width < 1 ||
@@ -699,7 +706,7 @@ static int launch_decode_mma(const ProjectionInput* proj, const void* q, int q_r
                          shared, stream, projection, (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, out_row_stride, \
                          scratch_o, scratch_ml, positions, token_seq, seq_seat, block_table, table_width,          \
                          (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, num_heads, group, chunks,   \
-                         num_kv_heads, page_size, page_shift, num_pages, window, key_chunk, keep_first, scale_log2, cluster_merge, error)
+                         num_kv_heads, page_size, page_shift, num_pages, window, key_chunk, keep_first, scale_log2, cluster_merge, extras, error)
 #define DISTIE_MMA_DECODE_BY_STAGES(DV, NV)   \
   if (stages == 2) { DISTIE_MMA_DECODE(DV, 2, NV) } \
   else { DISTIE_MMA_DECODE(DV, 3, NV) }
@@ -717,7 +724,7 @@ static int launch_decode_mma(const ProjectionInput* proj, const void* q, int q_r
     const dim3 merge_grid(tokens, num_heads);
     err = launch_dependent_family(8, attention_decode_mma_merge_kernel, merge_grid, dim3(kMergeThreads), 0, stream,
                            (const float*)scratch_o, (const float*)scratch_ml, (__nv_bfloat16*)out, out_row_stride,
-                           num_heads, head_dim, num_splits);
+                           num_heads, head_dim, num_splits, extras.sink);
     if (err != cudaSuccess) return (int)err;
   }
   return 0;
@@ -746,6 +753,21 @@ extern "C" int distie_attention_decode_mma_kept(const void* q, int q_row_stride,
   return launch_decode_mma(nullptr, q, q_row_stride, out, out_row_stride, scratch, positions, token_seq, seq_seat,
                            block_table, table_width, k_cache, v_cache, tokens, num_heads, num_kv_heads, head_dim,
                            page_size, num_pages, window, key_chunk, keep_first, scale, num_splits, error, stream);
+}
+
+// The same with capped scores (softcap > 0: s <- softcap * tanh(s / softcap) after the scale) and a sink per head
+// (float32 [num_heads] or null) whose exponential joins the softmax's denominator.
+extern "C" int distie_attention_decode_mma_capped(const void* q, int q_row_stride, void* out, int out_row_stride,
+                                                  float* scratch, const int* positions, const int* token_seq,
+                                                  const int* seq_seat, const int* block_table, int table_width,
+                                                  const void* k_cache, const void* v_cache, int tokens, int num_heads,
+                                                  int num_kv_heads, int head_dim, int page_size, int num_pages, int window,
+                                                  int key_chunk, int keep_first, float scale, float softcap,
+                                                  const float* sink, int num_splits, int* error, cudaStream_t stream) {
+  return launch_decode_mma(nullptr, q, q_row_stride, out, out_row_stride, scratch, positions, token_seq, seq_seat,
+                           block_table, table_width, k_cache, v_cache, tokens, num_heads, num_kv_heads, head_dim,
+                           page_size, num_pages, window, key_chunk, keep_first, scale, num_splits, error, stream,
+                           make_score_extras(scale, softcap, sink));
 }
 
 // The same for a step of single tokens that starts from the q/k/v projection: `slices` [splits, tokens, row_stride]

@@ -65,7 +65,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, 
                          const int* __restrict__ block_table, int table_width,
                          const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
                          int group_size, int num_kv_heads, int page_size, int page_shift, int num_pages,
-                         int window, int key_chunk, int keep_first, float scale_log2, int* __restrict__ error) {
+                         int window, int key_chunk, int keep_first, float scale_log2, const ScoreExtras extras,
+                         int* __restrict__ error) {
   constexpr int CHUNKS = D / 8;                       // 16-byte chunks per row
   constexpr int TILE_BYTES = kTileN * D * 2;
   constexpr int ROWS_PER_PASS = kPrefillWarps * 32 / CHUNKS;
@@ -189,6 +190,14 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, 
     // Only blocks that touch the diagonal or the window's edge need the per-element test: a block
     // is wholly visible to this warp when its last key is no later than the warp's first row and
     // its first key is inside the window of the warp's last row.
+    // With a cap the raw products become capped scores in base-2 units here, and nothing is left to multiply.
+    const float mult = extras.cap > 0.f ? 1.f : scale_log2;
+    if (extras.cap > 0.f) {
+#pragma unroll
+      for (int i = 0; i < kTileN / 8; ++i)
+#pragma unroll
+        for (int r = 0; r < 4; ++r) s[i][r] = capped_log2(s[i][r], extras);
+    }
     const int kb = block_key0(block);
     const int warp_first = p0 + warp * 16, warp_last = warp_first + 15;
     const bool whole = block >= sink_blocks && kb + kTileN - 1 <= warp_first &&
@@ -219,7 +228,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, 
       float m = tile_max[h];
       m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
       m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
-      const float m_new = fmaxf(row_max[h], m * scale_log2);
+      const float m_new = fmaxf(row_max[h], m * mult);
       corr[h] = (m_new == -INFINITY) ? 1.f : exp2f(row_max[h] - m_new);
       row_max[h] = m_new;
       row_sum[h] *= corr[h];
@@ -229,7 +238,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, 
     for (int i = 0; i < kTileN / 8; ++i) {
 #pragma unroll
       for (int r = 0; r < 4; ++r) {
-        const float p = exp2f(fmaf(s[i][r], scale_log2, shift[r >> 1]));  // exp2(-inf) = 0 for hidden keys
+        const float p = exp2f(fmaf(s[i][r], mult, shift[r >> 1]));  // exp2(-inf) = 0 for hidden keys
         s[i][r] = p;
         row_sum[r >> 1] += p;
       }
@@ -268,7 +277,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, 
     float l = row_sum[h];
     l += __shfl_xor_sync(0xffffffffu, l, 1);
     l += __shfl_xor_sync(0xffffffffu, l, 2);
-    const float inv = l > 0.f ? 1.f / l : 0.f;
+    const float inv = extras.sink ? sink_inverse_log2(row_max[h], l, extras.sink[head]) : (l > 0.f ? 1.f / l : 0.f);
     const int row = warp * 16 + g + 8 * h;
     if (row < rows) {
       __nv_bfloat16* dst = out + (size_t)(t0 + row) * out_row_stride + (size_t)head * D + 2 * c;
@@ -283,8 +292,8 @@ template <int D>
 int launch_prefill(const void* q, int q_row_stride, void* out, int out_row_stride, const int* q_tiles, int num_tiles,
                    const int* positions, const int* token_seq, const int* seq_seat, const int* block_table,
                    int table_width, const void* k_cache, const void* v_cache, int num_heads, int num_kv_heads,
-                   int page_size, int num_pages, int window, int key_chunk, int keep_first, float scale, int* error,
-                   cudaStream_t stream) {
+                   int page_size, int num_pages, int window, int key_chunk, int keep_first, float scale, float softcap,
+                   const float* sink, int* error, cudaStream_t stream) {
   const int shared = 4 * kTileN * D * 2;
   static bool configured = false;
   if (!configured) {
@@ -301,7 +310,7 @@ int launch_prefill(const void* q, int q_row_stride, void* out, int out_row_strid
       (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, out_row_stride, q_tiles, positions, token_seq,
       seq_seat, block_table, table_width, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
       num_heads / num_kv_heads, num_kv_heads, page_size, page_shift, num_pages, window, key_chunk, keep_first,
-      scale * 1.4426950408889634f, error);
+      scale * 1.4426950408889634f, make_score_extras(scale, softcap, sink), error);
   DISTIE_LAUNCH_CHECK();
   return 0;
 }
@@ -318,7 +327,7 @@ extern "C" int distie_attention_prefill(const void* q, int q_row_stride, void* o
                                         const int* token_seq, const int* seq_seat, const int* block_table,
                                         int table_width, const void* k_cache, const void* v_cache, int num_heads,
                                         int num_kv_heads, int head_dim, int page_size, int num_pages, int window, int key_chunk, int keep_first,
-                                        float scale, int* error, cudaStream_t stream) {
+                                        float scale, float softcap, const float* sink, int* error, cudaStream_t stream) {
   if (num_tiles <= 0) return 0;
   if (num_heads < 1 || num_kv_heads < 1 || num_heads % num_kv_heads != 0 || page_size < 1 || table_width < 1 ||
       2 * num_tiles > 65535 || (q_row_stride & 7) || (out_row_stride & 1))
@@ -326,7 +335,7 @@ extern "C" int distie_attention_prefill(const void* q, int q_row_stride, void* o
 #define DISTIE_PREFILL(DV)                                                                                        \
   return launch_prefill<DV>(q, q_row_stride, out, out_row_stride, q_tiles, num_tiles, positions, token_seq,       \
                             seq_seat, block_table, table_width, k_cache, v_cache, num_heads, num_kv_heads,        \
-                            page_size, num_pages, window, key_chunk, keep_first, scale, error, stream)
+                            page_size, num_pages, window, key_chunk, keep_first, scale, softcap, sink, error, stream)
   switch (head_dim) {
     case 64: DISTIE_PREFILL(64);
     case 128: DISTIE_PREFILL(128);

@@ -117,7 +117,10 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                                  const int* __restrict__ positions, const int* __restrict__ token_seq,
                                  const int* __restrict__ seq_seat, const int* __restrict__ block_table,
                                  int table_width, int group_size, int num_kv_heads, int page_shift, int num_pages,
-                                 int window, int key_chunk, int keep_first, float scale_log2, int* __restrict__ error) {
+                                 int window, int key_chunk, int keep_first, float scale_log2, float cap, float cap_pre,
+                                 const float* __restrict__ sink_logits, int* __restrict__ error) {
+  // cap > 0: a raw score s becomes cap * tanh(s * cap_pre) (cap_pre = scale / cap) and scale_log2 is log2(e) alone.
+  // sink_logits: one float per head whose exponential joins the row's sum at the end (null: none).
   extern __shared__ unsigned char raw[];
   auto& sm = *reinterpret_cast<AttnShared<D>*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
   constexpr int HALVES = D / 64;
@@ -327,6 +330,14 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       uint32_t sv[kAttnGroupKeys];
       tmem_load_64(s_addr, sv);
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      if (cap > 0.f) {  // tanh(x) = 1 - 2 / (exp(2x) + 1), on the fast exponential and reciprocal
+        const float twice = 2.f * 1.4426950408889634f * cap_pre;
+#pragma unroll
+        for (int i = 0; i < kAttnGroupKeys; ++i) {
+          const float e2 = exp2_approx(__uint_as_float(sv[i]) * twice);
+          sv[i] = __float_as_uint(cap - __fdividef(2.f * cap, e2 + 1.f));
+        }
+      }
       if (!unmasked) {
 #pragma unroll
         for (int i = 0; i < kAttnGroupKeys; ++i) {
@@ -420,7 +431,14 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       const float w0 = m0 == -INFINITY ? 0.f : exp2_approx(m0 - m_all);
       const float w1 = m1 == -INFINITY ? 0.f : exp2_approx(m1 - m_all);
       const float l_all = sm.row_sum[0][r] * w0 + sm.row_sum[1][r] * w1;
-      const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+      float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+      if (sink_logits) {  // one more term in the sum, taken around the larger of the maximum and the sink
+        const float sk = sink_logits[head] * 1.4426950408889634f;
+        const float top = fmaxf(m_all, sk);
+        const float keys = m_all == -INFINITY ? 0.f : exp2_approx(m_all - top);
+        const float total = l_all * keys + exp2_approx(sk - top);
+        inv = total > 0.f ? keys / total : 0.f;
+      }
       const float f0 = w0 * inv, f1 = w1 * inv;
       // Group g writes columns g * D / 2 ... of the row, from both accumulators.  A whole tile of 128 rows goes
       // into the shared memory that held Q (all products with Q are done), in the layout of a tile copy, and
@@ -490,7 +508,7 @@ static int launch_attention_tc(const CUtensorMap& map_q, const CUtensorMap& map_
                                int out_row_stride, const int* q_tiles, int num_tiles, const int* positions,
                                const int* token_seq, const int* seq_seat, const int* block_table, int table_width,
                                int num_heads, int num_kv_heads, int page_shift, int num_pages, int window, int key_chunk, int keep_first,
-                               float scale_log2, int* error, cudaStream_t stream) {
+                               float scale_log2, float cap, float cap_pre, const float* sink, int* error, cudaStream_t stream) {
   const size_t shared = sizeof(AttnShared<D>) + 1024;
   static bool configured = false;
   if (!configured) {
@@ -503,7 +521,7 @@ static int launch_attention_tc(const CUtensorMap& map_q, const CUtensorMap& map_
       32, attention_prefill_tcgen05_kernel<D>, dim3(num_heads, num_tiles), dim3(kAttnThreads), shared, stream, map_q,
       map_k, map_v, map_out, (__nv_bfloat16*)out, out_row_stride, q_tiles, positions, token_seq, seq_seat, block_table,
       table_width, num_heads / num_kv_heads, num_kv_heads, page_shift, num_pages, window, key_chunk, keep_first, scale_log2,
-      error);
+      cap, cap_pre, sink, error);
   return err == cudaSuccess ? 0 : (int)err;
 }
 
@@ -521,7 +539,7 @@ extern "C" int distie_attention_prefill_tcgen05(const void* q, int q_row_stride,
                                                 int table_width, const void* k_cache, const void* v_cache, int tokens,
                                                 int num_heads, int num_kv_heads, int head_dim, int page_size,
                                                 int num_pages, int window, int key_chunk, int keep_first, float scale,
-                                                int* error, cudaStream_t stream) {
+                                                float softcap, const float* sink, int* error, cudaStream_t stream) {
   if (num_tiles <= 0) return 0;
   if (tokens < 1 || num_heads < 1 || num_kv_heads < 1 || num_heads % num_kv_heads != 0 || table_width < 1 ||
       num_pages < 1 || num_tiles > 65535 || keep_first < 0)
@@ -540,12 +558,13 @@ extern "C" int distie_attention_prefill_tcgen05(const void* q, int q_row_stride,
   if (cache_rows > 0x7fffffffLL) return DISTIE_ERR_UNSUPPORTED;
   if ((status = make_map(&map_k, k_cache, (int)cache_rows, head_dim, head_dim, page_size)) != 0) return status;
   if ((status = make_map(&map_v, v_cache, (int)cache_rows, head_dim, head_dim, page_size)) != 0) return status;
-  const float scale_log2 = scale * 1.4426950408889634f;
+  const float cap = softcap > 0.f ? softcap : 0.f, cap_pre = cap > 0.f ? scale / cap : 0.f;
+  const float scale_log2 = (cap > 0.f ? 1.f : scale) * 1.4426950408889634f;
   if (head_dim == 64)
     return launch_attention_tc<64>(map_q, map_k, map_v, map_out, out, out_row_stride, q_tiles, num_tiles, positions, token_seq,
                                    seq_seat, block_table, table_width, num_heads, num_kv_heads, page_shift, num_pages,
-                                   window, key_chunk, keep_first, scale_log2, error, stream);
+                                   window, key_chunk, keep_first, scale_log2, cap, cap_pre, sink, error, stream);
   return launch_attention_tc<128>(map_q, map_k, map_v, map_out, out, out_row_stride, q_tiles, num_tiles, positions, token_seq,
                                   seq_seat, block_table, table_width, num_heads, num_kv_heads, page_shift, num_pages,
-                                  window, key_chunk, keep_first, scale_log2, error, stream);
+                                  window, key_chunk, keep_first, scale_log2, cap, cap_pre, sink, error, stream);
 }

@@ -79,6 +79,37 @@ __device__ __forceinline__ float sink_inverse(float m, float l, float sink) {
   return total > 0.f ? keys / total : 0.f;
 }
 
+// The same with the maximum in base-2 units (kernels whose exponentials are exp2): m2 = log2(e) * maximum.
+__device__ __forceinline__ float sink_inverse_log2(float m2, float l, float sink) {
+  const float sk = sink * 1.4426950408889634f;
+  const float top = fmaxf(m2, sk);
+  const float keys = m2 == -INFINITY ? 0.f : exp2f(m2 - top);
+  const float total = l * keys + exp2f(sk - top);
+  return total > 0.f ? keys / total : 0.f;
+}
+
+// What a softmax attention kernel may be asked beyond scale and mask: cap > 0 caps a scaled score s to
+// cap * tanh(s / cap) (cap_pre = scale / cap multiplies the raw product); sink, one float per head, joins the
+// denominator as exp(sink).  All zero: an ordinary softmax.
+struct ScoreExtras {
+  float cap = 0.f;
+  float cap_pre = 0.f;
+  const float* sink = nullptr;
+};
+__host__ inline ScoreExtras make_score_extras(float scale, float softcap, const float* sink) {
+  ScoreExtras e;
+  e.cap = softcap > 0.f ? softcap : 0.f;
+  e.cap_pre = e.cap > 0.f ? scale / e.cap : 0.f;
+  e.sink = sink;
+  return e;
+}
+// The capped score in base-2 units from the raw product `s`: log2(e) * cap * tanh(s * cap_pre), with
+// tanh(x) = 1 - 2 / (exp(2x) + 1) on the fast exponential.
+__device__ __forceinline__ float capped_log2(float s, const ScoreExtras& x) {
+  const float e2 = exp2f(s * (2.f * 1.4426950408889634f * x.cap_pre));
+  return (x.cap - __fdividef(2.f * x.cap, e2 + 1.f)) * 1.4426950408889634f;
+}
+
 // Sum over a block of up to 1024 threads; `scratch` holds 32 floats of shared memory.
 // Every thread gets the result.  Safe to call repeatedly with the same scratch.
 __device__ __forceinline__ float block_sum(float v, float* scratch) {

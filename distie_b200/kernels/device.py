@@ -395,14 +395,14 @@ class DeviceKernels(KernelSet):
         sink_ptr = sink.data_ptr() if sink is not None else None
         if sink is not None and (sink.dtype != torch.float32 or sink.numel() != num_heads or not sink.is_contiguous()):
             raise KernelError("attention: the sink is one float32 per head")
-        extras = softcap > 0.0 or sink is not None  # served by the kernels on the FMA pipe
+        extras = softcap > 0.0 or sink is not None
         value_dim = kv.v.shape[-1]
         same = value_dim == head_dim  # every kernel but the size-agnostic one wants values as large as keys
         n_dec = step.num_decode_tokens if head_dim in _DECODE_HEAD_DIMS and same else 0
         element = qkv.element_size()
         if n_dec > 0:
             splits = self.plan_splits(n_dec, num_heads, num_kv_heads, step.max_kv_len)
-            tensor_cores = self.dtype == torch.bfloat16 and head_dim in _PREFILL_HEAD_DIMS and not extras
+            tensor_cores = self.dtype == torch.bfloat16 and head_dim in _PREFILL_HEAD_DIMS
             if tensor_cores and splits <= 2 * _CLUSTER_SPLITS:
                 splits = min(splits, _CLUSTER_SPLITS)  # merged inside the kernel, by a cluster of CTAs
             in_kernel_merge = splits == 1 or (tensor_cores and splits <= _CLUSTER_SPLITS)
@@ -417,7 +417,13 @@ class DeviceKernels(KernelSet):
                 kv.block_table.shape[-1], kv.k.data_ptr(), kv.v.data_ptr(), n_dec, num_heads, num_kv_heads,
                 head_dim, kv.page_size, kv.num_pages, window, chunk,
             ]
-            if tensor_cores:
+            if tensor_cores and extras:
+                check(
+                    function("distie_attention_decode_mma_capped")(*head, keep_first, float(scale), softcap, sink_ptr, splits,
+                                                                   self.error_flag.data_ptr(), self._stream()),
+                    "attention_decode_mma",
+                )
+            elif tensor_cores:
                 check(
                     function("distie_attention_decode_mma_kept")(*head, keep_first, float(scale), splits,
                                                                  self.error_flag.data_ptr(), self._stream()),
@@ -432,9 +438,9 @@ class DeviceKernels(KernelSet):
             self._ran("attention_decode_mma" if tensor_cores else "attention_decode", 1 if in_kernel_merge else 2)
         rest = step.num_tokens - n_dec
         tiled = (rest > 0 and self.dtype == torch.bfloat16 and head_dim in _PREFILL_HEAD_DIMS and step.num_q_tiles
-                 and n_dec == step.num_decode_tokens and same and not extras)
+                 and n_dec == step.num_decode_tokens and same)
         if tiled and self._attention_tcgen05(qkv, out, step, kv, num_heads, num_kv_heads, head_dim, window, chunk, scale,
-                                             keep_first):
+                                             keep_first, softcap, sink_ptr):
             pass
         elif tiled:
             check(
@@ -443,7 +449,7 @@ class DeviceKernels(KernelSet):
                     step.num_q_tiles, step.positions.data_ptr(), step.token_seq.data_ptr(), step.seq_seat.data_ptr(),
                     kv.block_table.data_ptr(), kv.block_table.shape[-1], kv.k.data_ptr(), kv.v.data_ptr(), num_heads,
                     num_kv_heads, head_dim, kv.page_size, kv.num_pages, window, chunk, keep_first, float(scale),
-                    self.error_flag.data_ptr(), self._stream(),
+                    softcap, sink_ptr, self.error_flag.data_ptr(), self._stream(),
                 ),
                 "attention_prefill",
             )
@@ -464,14 +470,14 @@ class DeviceKernels(KernelSet):
             self._ran("attention_generic")
 
     def _attention_tcgen05(self, qkv, out, step, kv, num_heads, num_kv_heads, head_dim, window, chunk, scale,
-                           keep_first=0) -> bool:
+                           keep_first=0, softcap=0.0, sink_ptr=None) -> bool:
         """Prompt portions on the tcgen05 kernel; False when it refuses the page size or an alignment."""
         code = function("distie_attention_prefill_tcgen05")(
             qkv.data_ptr(), qkv.stride(0), out.data_ptr(), out.stride(0), step.q_tiles.data_ptr(), step.num_q_tiles,
             step.positions.data_ptr(), step.token_seq.data_ptr(), step.seq_seat.data_ptr(),
             kv.block_table.data_ptr(), kv.block_table.shape[-1], kv.k.data_ptr(), kv.v.data_ptr(), qkv.shape[0],
             num_heads, num_kv_heads, head_dim, kv.page_size, kv.num_pages, window, chunk, keep_first, float(scale),
-            self.error_flag.data_ptr(), self._stream(),
+            float(softcap), sink_ptr, self.error_flag.data_ptr(), self._stream(),
         )
         if code == -2:
             return False

@@ -41,14 +41,17 @@ _SIGNATURES: dict[str, tuple[str, list]] = {
     ),
     "distie_attention_decode_scratch_floats": ("base", [I, I, I, I]),
     "distie_sample": ("base", [P, L, I, I, P, P, P, P]),
-    "distie_attention_prefill": ("bf16", [P, I, P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, F, P, P]),
+    "distie_attention_prefill": ("bf16", [P, I, P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, F, F, P, P, P]),
     "distie_attention_prefill_tile": ("bf16", []),
     "distie_attention_prefill_tcgen05": (
-        "bf16", [P, I, P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, I, F, P, P]
+        "bf16", [P, I, P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, I, F, F, P, P, P]
     ),
     "distie_attention_decode_mma_stages": ("bf16", [I, I, I, I]),
     "distie_attention_decode_mma": ("bf16", [P, I, P, I, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, F, I, P, P]),
     "distie_attention_decode_mma_kept": ("bf16", [P, I, P, I, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, I, F, I, P, P]),
+    "distie_attention_decode_mma_capped": (
+        "bf16", [P, I, P, I, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, I, F, F, P, I, P, P]
+    ),
     "distie_attention_decode_mma_qkv": (
         "bf16", [P, I, L, I, P, P, F, I, P, I, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, F, I, P, P]
     ),

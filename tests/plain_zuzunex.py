@@ -177,11 +177,12 @@ def choose_experts(scores, correction, top):
 
 
 def choice_margin(scores, correction, top):
-    """Per token the gap between the last chosen and the first not chosen choice score."""
+    """Per token the gap between the last chosen and the first not chosen choice score, as a share of the former's
+    size (what rounding does to a score grows with the score)."""
     ranked = (scores + correction).sort(-1, descending=True).values
     if ranked.shape[-1] <= top:
         return torch.full(ranked.shape[:-1], float("inf"))
-    return ranked[..., top - 1] - ranked[..., top]
+    return (ranked[..., top - 1] - ranked[..., top]) / ranked[..., top - 1].abs().clamp_min(1e-30)
 
 
 def routed_ff(h, w, p, mlp, margins=None):
