@@ -33,7 +33,8 @@ time per output token, preemptions and the step-time split; ``--dtype fp32`` tim
 true 32-bit engine.  Their caches are sized from free device memory.  ``--compare zelasun`` times the
 Zelasun design beside the Qwen2 decoder at equal width, feed-forward, heads and depth (prefill of 2,048
 tokens, decode steps at ``--batch``; the time of a layer from two depths) and prints a line of its own;
-``--compare fovudra`` does the same for the Fovudra design beside Zelasun and Qwen2.
+``--compare fovudra`` does the same for the Fovudra design beside Zelasun and Qwen2, ``--compare zururax`` and
+``--compare zuzunex`` for those designs beside Fovudra and Qwen2.
 """
 
 from __future__ import annotations
@@ -278,6 +279,25 @@ def zururax_config(size: dict, layers: int) -> dict:
             "embedding": {"scale": 1.0}, "layers": [layer(i) for i in range(layers)]}
 
 
+def zuzunex_config(size: dict, layers: int) -> dict:
+    """The Zuzunex design at a Qwen2.5 layer's width and heads: heads of 128 for keys and values; layers alternate
+    between attention without rotation (unit-normed q and k, a query temperature that steps every 1,024 positions,
+    scores capped at 30) and attention behind a convolution of four taps (biases, weighted norms, half of each head
+    rotated with slowed long waves); every layer has the sink and the output gate.  Feed-forwards alternate in pairs
+    between the dense one and a routed one whose active part equals it (16 experts of a quarter of the dense width and
+    two that return their input, three per token, beside a shared expert of the same size)."""
+    heads, kv, quarter = size["heads"], size["kv_heads"], size["ff"] // 4
+    moe = {"kind": "moe", "router": {"experts": 16, "identity": 2, "top": 3}, "expert": {"ff": quarter}, "shared": {"ff": quarter}}
+    dense = {"kind": "dense", "ff": size["ff"]}
+    common = {"heads": heads, "kv_heads": kv, "dim": 128, "vdim": 128, "scale": 128 ** -0.5}
+    plain = {"type": "attention", "mixer": {**common, "softcap": 30.0, "q_temp": {"coef": 0.1, "every": 1024}}}
+    conv = {"type": "attention_2", "mixer": {**common, "conv": 4, "rot": {
+        "base": 1e6, "dims": 64, "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}}}
+    pattern = [{**plain, "mlp": dense}, {**conv, "mlp": moe}, {**plain, "mlp": moe}, {**conv, "mlp": dense}]
+    return {"architecture": "Zuzunex", "vocab": COMPARE_VOCAB, "width": size["width"], "norm": {"eps": 1e-6},
+            "logit_scale": 1.0, "layers": [pattern[i % 4] for i in range(layers)]}
+
+
 def qwen2_config(size: dict, layers: int) -> dict:
     return {"architectures": ["Qwen2ForCausalLM"], "vocab_size": COMPARE_VOCAB, "hidden_size": size["width"],
             "intermediate_size": size["ff"], "num_hidden_layers": layers, "num_attention_heads": size["heads"],
@@ -286,7 +306,7 @@ def qwen2_config(size: dict, layers: int) -> dict:
 
 
 def compare_designs(args) -> int:
-    """``--compare zelasun`` (or ``fovudra``, ``zururax``): prefill of 2,048 tokens and decode steps at batch ``--batch`` behind
+    """``--compare zelasun`` (or ``fovudra``, ``zururax``, ``zuzunex``): prefill of 2,048 tokens and decode steps at batch ``--batch`` behind
     1,024-token prompts, for the named design beside the Qwen2 decoder (and, for Fovudra, beside Zelasun, the other
     design with recurrences; for Zururax, beside Fovudra, the other design with routed experts) at equal width, feed-forward, heads and depth.  Each model is
     built at two depths (4 and 8 layers) so that the time of a layer is the difference, free of embedding and head.
@@ -303,12 +323,13 @@ def compare_designs(args) -> int:
     dtype = "bfloat16" if args.dtype == "bf16" else "float32"
     depths = (4, 8) if args.layers is None else (args.layers,)
     designs = {"zelasun": ("zelasun", "qwen2"), "fovudra": ("fovudra", "zelasun", "qwen2"),
-               "zururax": ("zururax", "fovudra", "qwen2")}[args.compare]
+               "zururax": ("zururax", "fovudra", "qwen2"), "zuzunex": ("zuzunex", "fovudra", "qwen2")}[args.compare]
     if args.designs:
         designs = tuple(d for d in designs if d in args.designs.split(","))
     configs = {"zelasun": lambda size, depth: zelasun_config(size, depth, args.chunk),
                "fovudra": lambda size, depth: fovudra_config(size, depth, args.chunk),
                "zururax": lambda size, depth: zururax_config(size, depth),
+               "zuzunex": lambda size, depth: zuzunex_config(size, depth),
                "qwen2": lambda size, depth: qwen2_config(size, depth)}
     out = {"compare": " beside ".join(designs), "dtype": args.dtype, "batch": args.batch, "prompt_len": PROMPT_LEN,
            "prefill_tokens": PREFILL_TOKENS, "chunk": args.chunk, "sizes": {}}
@@ -568,7 +589,7 @@ def main() -> int:
                         help="with --impl reference: its attention backend (default: DISTIE_ATTN, else auto)")
     parser.add_argument("--ref-device", default=None, help=argparse.SUPPRESS)  # "cpu": a dry run of the reference arm
     parser.add_argument("--designs", default=None, help="with --compare: only these of its designs, with commas between them")
-    parser.add_argument("--compare", default=None, choices=["zelasun", "fovudra", "zururax"],
+    parser.add_argument("--compare", default=None, choices=["zelasun", "fovudra", "zururax", "zuzunex"],
                         help="time another design beside the Qwen2 decoder at equal layer sizes instead of the default run")
     parser.add_argument("--chunk", type=int, default=1024,
                         help="with --compare: the chunk (Zelasun) or window (Fovudra) of the design's attention")

@@ -330,13 +330,9 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       uint32_t sv[kAttnGroupKeys];
       tmem_load_64(s_addr, sv);
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      if (cap > 0.f) {  // tanh(x) = 1 - 2 / (exp(2x) + 1), on the fast exponential and reciprocal
-        const float twice = 2.f * 1.4426950408889634f * cap_pre;
+      if (cap > 0.f) {  // one more special-function instruction per score
 #pragma unroll
-        for (int i = 0; i < kAttnGroupKeys; ++i) {
-          const float e2 = exp2_approx(__uint_as_float(sv[i]) * twice);
-          sv[i] = __float_as_uint(cap - __fdividef(2.f * cap, e2 + 1.f));
-        }
+        for (int i = 0; i < kAttnGroupKeys; ++i) sv[i] = __float_as_uint(cap * tanh_fast(__uint_as_float(sv[i]) * cap_pre));
       }
       if (!unmasked) {
 #pragma unroll

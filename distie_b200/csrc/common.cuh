@@ -62,12 +62,6 @@ __host__ __device__ __forceinline__ int first_visible_key(int pos, int window, i
 
 // A cap on a score: cap * tanh(s / cap) with cap > 0; cap <= 0 leaves the score as it is.
 __device__ __forceinline__ float cap_score(float s, float cap) { return cap > 0.f ? cap * tanhf(s / cap) : s; }
-// The same for kernels that serve in 16 bits: tanh(x) = 1 - 2 / (exp(2x) + 1) on the fast exponential
-// (relative error of the order of 1e-6, exact limits at both ends).
-__device__ __forceinline__ float cap_score_fast(float s, float cap) {
-  if (cap <= 0.f) return s;
-  return cap * (1.f - __fdividef(2.f, __expf(2.f * s / cap) + 1.f));
-}
 
 // A sink in a softmax: one more term exp(sink) in the denominator that has no value.  Given the running maximum `m`
 // and sum `l` over the keys (sum of exp(s - m)), returns the factor the mix (sum of exp(s - m) v) is multiplied by:
@@ -103,11 +97,17 @@ __host__ inline ScoreExtras make_score_extras(float scale, float softcap, const 
   e.sink = sink;
   return e;
 }
-// The capped score in base-2 units from the raw product `s`: log2(e) * cap * tanh(s * cap_pre), with
-// tanh(x) = 1 - 2 / (exp(2x) + 1) on the fast exponential.
+// The hardware's tanh (one instruction of the special-function unit; relative error about 2^-11, which in a capped
+// score stays below what the 16-bit q and k that the tensor-core kernels multiply have already cost).
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// The capped score in base-2 units from the raw product `s`: log2(e) * cap * tanh(s * cap_pre); for the kernels that
+// serve in 16 bits.
 __device__ __forceinline__ float capped_log2(float s, const ScoreExtras& x) {
-  const float e2 = exp2f(s * (2.f * 1.4426950408889634f * x.cap_pre));
-  return (x.cap - __fdividef(2.f * x.cap, e2 + 1.f)) * 1.4426950408889634f;
+  return (x.cap * 1.4426950408889634f) * tanh_fast(s * x.cap_pre);
 }
 
 // Sum over a block of up to 1024 threads; `scratch` holds 32 floats of shared memory.

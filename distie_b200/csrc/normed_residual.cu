@@ -1,5 +1,6 @@
-// Two kernels of layers that norm a sublayer's output before it joins the residual and whose attention
-// keeps a token's key as its value:
+// Kernels between a product's float32 accumulators and what reads them: of layers that norm a sublayer's output before
+// it joins the residual and whose attention keeps a token's key as its value, and of layers that norm q and k before
+// they rotate them:
 //
 //  * norm_add_rmsnorm: d = sum_j scale_j * term_j (float32); residual += d * rsqrt(mean(d^2) + eps_d) * w_d
 //    (or += d when there is no w_d), written back; out = residual * rsqrt(mean(residual^2) + eps) * w, cast
@@ -8,6 +9,9 @@
 //    bias: the key as projected is stored as the value; q and k are rotated over the first `rotary_dim`
 //    elements of each head (angles pos * inv_freq in float32), then each head is divided by its root mean
 //    square; k goes to its page and q to its buffer.  One block per token, a warp per head.
+//  * qkv_norm_write: from the float32 projection [q | k | v] plus bias: every head of q and k divided by its root mean
+//    square (and multiplied by a weight shared by the heads), THEN rotated; q times a temperature that grows with the
+//    logarithm of the position; k and v (values of a size of their own) to their pages, q to its buffer.
 //
 // All arithmetic is float32; T is the type of what is stored for the next product or in the cache.
 #include "common.cuh"
