@@ -277,12 +277,15 @@ extern "C" long long distie_attention_decode_scratch_floats(int tokens, int num_
   return (long long)tokens * num_heads * num_splits * (head_dim + 2);
 }
 
-extern "C" int distie_attention_decode(const void* q, int q_row_stride, void* out, int out_row_stride,
-                                       float* scratch, const int* positions, const int* token_seq,
-                                       const int* seq_seat, const int* block_table, int table_width,
-                                       const void* k_cache, const void* v_cache, int tokens, int num_heads,
-                                       int num_kv_heads, int head_dim, int page_size, int num_pages, int window, int key_chunk,
-                                       int keep_first, float scale, float softcap, const float* sink, int num_splits, int dtype, int* error, cudaStream_t stream) {
+// The attention with what a softmax may be asked beyond scale and mask: softcap > 0 caps a scaled score s to
+// softcap * tanh(s / softcap); sink (float32 [num_heads] or null) joins the denominator as exp(sink_h).
+extern "C" int distie_attention_decode_capped(const void* q, int q_row_stride, void* out, int out_row_stride,
+                                              float* scratch, const int* positions, const int* token_seq,
+                                              const int* seq_seat, const int* block_table, int table_width,
+                                              const void* k_cache, const void* v_cache, int tokens, int num_heads,
+                                              int num_kv_heads, int head_dim, int page_size, int num_pages, int window,
+                                              int key_chunk, int keep_first, float scale, float softcap, const float* sink,
+                                              int num_splits, int dtype, int* error, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (num_heads < 1 || num_kv_heads < 1 || num_heads % num_kv_heads != 0 || page_size < 1 || table_width < 1 ||
       num_splits < 1 || num_splits > 65535 || (num_splits > 1 && scratch == nullptr) || keep_first < 0)
@@ -299,6 +302,19 @@ extern "C" int distie_attention_decode(const void* q, int q_row_stride, void* ou
                                   token_seq, seq_seat, block_table, table_width, k_cache, v_cache, tokens, num_heads,
                                   num_kv_heads, page_size, num_pages, window, key_chunk, keep_first, scale, softcap, sink, num_splits, error, stream);
   return DISTIE_ERR_UNSUPPORTED;
+}
+
+// The ordinary softmax: no cap, no sink.  (Callers outside this package bind this signature; it stays as it is.)
+extern "C" int distie_attention_decode(const void* q, int q_row_stride, void* out, int out_row_stride,
+                                       float* scratch, const int* positions, const int* token_seq,
+                                       const int* seq_seat, const int* block_table, int table_width,
+                                       const void* k_cache, const void* v_cache, int tokens, int num_heads,
+                                       int num_kv_heads, int head_dim, int page_size, int num_pages, int window, int key_chunk,
+                                       int keep_first, float scale, int num_splits, int dtype, int* error, cudaStream_t stream) {
+  return distie_attention_decode_capped(q, q_row_stride, out, out_row_stride, scratch, positions, token_seq, seq_seat,
+                                        block_table, table_width, k_cache, v_cache, tokens, num_heads, num_kv_heads, head_dim,
+                                        page_size, num_pages, window, key_chunk, keep_first, scale, 0.f, nullptr, num_splits,
+                                        dtype, error, stream);
 }
 
 // ---------------------------------------------------------------------------
@@ -366,5 +382,5 @@ extern "C" int distie_attention_decode_static(const void* q, int q_row_stride, v
   // (max, sum, mix) of every (token, head, split) before the merge kernel reads it.
   return distie_attention_decode(q, q_row_stride, out, out_row_stride, scratch, positions, token_seq, seq_seat,
                                  block_table, table_width, k_cache, v_cache, tokens, num_heads, num_kv_heads, head_dim,
-                                 page_size, num_pages, window, /*key_chunk=*/0, /*keep_first=*/0, scale, /*softcap=*/0.f, /*sink=*/nullptr, num_splits, dtype, error, stream);
+                                 page_size, num_pages, window, /*key_chunk=*/0, /*keep_first=*/0, scale, num_splits, dtype, error, stream);
 }

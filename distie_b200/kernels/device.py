@@ -431,7 +431,7 @@ class DeviceKernels(KernelSet):
                 )
             else:
                 check(
-                    function("distie_attention_decode")(*head, keep_first, float(scale), softcap, sink_ptr, splits, self.code,
+                    function("distie_attention_decode_capped")(*head, keep_first, float(scale), softcap, sink_ptr, splits, self.code,
                                                         self.error_flag.data_ptr(), self._stream()),
                     "attention_decode",
                 )

@@ -31,7 +31,8 @@ _SIGNATURES: dict[str, tuple[str, list]] = {
     "distie_rope_rows": ("base", [P, P, P, P, I, P, F, I, I, I, I, I, P, P, P, P]),
     "distie_bias_cast": ("base", [P, P, P, L, I, I, P]),
     "distie_attention_generic": ("base", [P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, I, I, F, F, P, I, P, P]),
-    "distie_attention_decode": ("base", [P, I, P, I, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, I, F, F, P, I, I, P, P]),
+    "distie_attention_decode": ("base", [P, I, P, I, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, I, F, I, I, P, P]),
+    "distie_attention_decode_capped": ("base", [P, I, P, I, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, I, F, F, P, I, I, P, P]),
     "distie_qkv_norm_write": (
         "base", [P, I, I, L, P, P, I, P, P, P, P, I, P, F, P, P, I, I, I, I, I, I, I, I, I, I, I, F, P, P, F, I, I, P, P]
     ),
