@@ -56,7 +56,7 @@ class SinkAttentionSizes:
     scale: float
     softcap: float | None = None        # scores become cap * tanh(score / cap)
     temp_coef: float | None = None      # q times 1 + coef * ln(floor((p + 1) / every) + 1)
-    temp_every: int | None = None
+    temp_every: float | None = None     # a positive number, usually whole
     biases: bool = False                # q, k and v have biases
     weighted_norm: bool = False         # the norm of q and k has a weight (shared by the heads)
     conv: int | None = None             # taps of the causal convolution behind the projections
@@ -73,11 +73,13 @@ class SinkAttentionSizes:
         if kind == "attention":
             temp = _optional(raw, "q_temp")
             cap = _optional(raw, "softcap")
+            if temp is not None and _number(temp, "every", where + "q_temp.") <= 0:
+                raise ConfigError(f"{where}q_temp.every must be positive")
             if cap is not None and _number(raw, "softcap", where) <= 0:
                 raise ConfigError(f"{where}softcap must be positive")
             return cls(**common, softcap=float(cap) if cap is not None else None,
                        temp_coef=_number(temp, "coef", where + "q_temp.") if temp is not None else None,
-                       temp_every=_count(temp, "every", where + "q_temp.") if temp is not None else None)
+                       temp_every=_number(temp, "every", where + "q_temp.") if temp is not None else None)
         rot, taps = _optional(raw, "rot"), _optional(raw, "conv")
         scaling = _optional(rot, "scaling")
         out = cls(**common, biases=True, weighted_norm=True,

@@ -211,7 +211,7 @@ qk_rope_norm_write_kernel(SlicedRows qk, const float* __restrict__ bias, T* __re
 // heads, in this order: bias; with `normed` the division by the head's root mean square (eps inside the root) and,
 // where a weight is given, the multiplication by it (head_dim floats shared by the heads); the rotation of the
 // first rotary_dim elements; for q the temperature 1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1)
-// (temp_every > 0).  v heads (value_dim elements, which may differ from head_dim) get their bias and are stored.
+// (temp_every > 0; the quotient of two floats is exact wherever it is whole, for positions below 2^24).  v heads (value_dim elements, which may differ from head_dim) get their bias and are stored.
 template <typename T>
 __global__ void __launch_bounds__(kRopeWarps * 32)
 qkv_norm_write_kernel(SlicedRows qkv, const float* __restrict__ bias, T* __restrict__ q_out, int q_out_stride,
@@ -221,7 +221,7 @@ qkv_norm_write_kernel(SlicedRows qkv, const float* __restrict__ bias, T* __restr
                       int num_heads, int num_kv_heads, int head_dim, int value_dim, int rotary_dim, int interleaved,
                       int page_size, int num_pages, int write, int normed, float norm_eps,
                       const float* __restrict__ q_weight, const float* __restrict__ k_weight, float temp_coef,
-                      int temp_every, int* __restrict__ error) {
+                      float temp_every, int* __restrict__ error) {
   extern __shared__ __align__(16) float heads_s[];  // kRopeWarps pieces of `piece` floats, then cos and sin of the token
   const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int piece = max(head_dim, value_dim);
@@ -247,7 +247,7 @@ qkv_norm_write_kernel(SlicedRows qkv, const float* __restrict__ bias, T* __restr
       page = -1;
     }
   }
-  const float temperature = temp_every > 0 ? 1.f + temp_coef * logf((float)((pos + 1) / temp_every) + 1.f) : 1.f;
+  const float temperature = temp_every > 0.f ? 1.f + temp_coef * logf(floorf((float)(pos + 1) / temp_every) + 1.f) : 1.f;
   const int k_column0 = num_heads * head_dim, v_column0 = (num_heads + num_kv_heads) * head_dim;
   const int heads_here = num_heads + (write ? 2 * num_kv_heads : 0);
   for (int head = blockIdx.y * kRopeWarps + warp; head < heads_here; head += gridDim.y * kRopeWarps) {
@@ -393,7 +393,7 @@ extern "C" int distie_qkv_norm_write(const float* qkv, int qkv_stride, int split
                                      float factor, void* k_cache, void* v_cache, int tokens, int num_heads, int num_kv_heads,
                                      int head_dim, int value_dim, int rotary_dim, int interleaved, int page_size,
                                      int num_pages, int write, int normed, float norm_eps, const float* q_weight,
-                                     const float* k_weight, float temp_coef, int temp_every, int dtype, int* error,
+                                     const float* k_weight, float temp_coef, float temp_every, int dtype, int* error,
                                      cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (num_heads < 1 || num_kv_heads < 1 || head_dim < 1 || head_dim > 1024 || value_dim < 1 || value_dim > 1024 ||

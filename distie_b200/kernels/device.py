@@ -672,7 +672,7 @@ class DeviceKernels(KernelSet):
         if write and (kv.k.dtype != q_out.dtype or kv.v.shape[-1] != value_dim or kv.k.shape[-1] != head_dim):
             raise KernelError("qkv_norm_write: the cache holds keys of head_dim and values of value_dim, of q's type")
         table = kv.block_table if write else step.seq_seat
-        coef, every = (float(q_temp[0]), int(q_temp[1])) if q_temp else (0.0, 0)
+        coef, every = (float(q_temp[0]), float(q_temp[1])) if q_temp else (0.0, 0.0)
         check(
             function("distie_qkv_norm_write")(
                 *self._sliced(qkv, "qkv_norm_write"), bias.data_ptr() if bias is not None else None, q_out.data_ptr(),

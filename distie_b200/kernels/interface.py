@@ -217,7 +217,7 @@ class KernelSet(ABC):
         With ``norm_eps`` every head of q and k is divided by its root mean square over ``head_dim`` (eps inside
         the root) and, with ``q_weight`` / ``k_weight`` (float32 ``[head_dim]``), multiplied by it; THEN q and k are
         rotated (``rotary``); with ``q_temp = (coef, every)`` q at position p is multiplied by
-        ``1 + coef * ln(floor((p + 1) / every) + 1)``.  k and v go to their pages (if ``kv``; values may have
+        ``1 + coef * ln(floor((p + 1) / every) + 1)`` (``every`` a positive number).  k and v go to their pages (if ``kv``; values may have
         another size than keys) and q to ``q_out [T, heads * head_dim]`` in the set's dtype.  All float32."""
         raise NotImplementedError
 

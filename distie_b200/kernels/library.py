@@ -34,7 +34,7 @@ _SIGNATURES: dict[str, tuple[str, list]] = {
     "distie_attention_decode": ("base", [P, I, P, I, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, I, F, I, I, P, P]),
     "distie_attention_decode_capped": ("base", [P, I, P, I, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, I, F, F, P, I, I, P, P]),
     "distie_qkv_norm_write": (
-        "base", [P, I, I, L, P, P, I, P, P, P, P, I, P, F, P, P, I, I, I, I, I, I, I, I, I, I, I, F, P, P, F, I, I, P, P]
+        "base", [P, I, I, L, P, P, I, P, P, P, P, I, P, F, P, P, I, I, I, I, I, I, I, I, I, I, I, F, P, P, F, F, I, P, P]
     ),
     "distie_norm_add_rmsnorm": ("base", [P, P, I, P, F, P, P, F, P, P, I, I, I, P]),
     "distie_qk_rope_norm_write": (

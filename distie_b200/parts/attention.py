@@ -125,8 +125,8 @@ class GqaAttention:
                 raise ValueError("norm_weights goes with norm_first")
             if params.get("softcap") is not None and float(params["softcap"]) <= 0:
                 raise ValueError(f"softcap must be positive, got {params['softcap']}")
-            if params.get("q_temp") and int(params["q_temp"][1]) < 1:
-                raise ValueError("q_temp = (coef, every) with every >= 1")
+            if params.get("q_temp") and float(params["q_temp"][1]) <= 0:
+                raise ValueError("q_temp = (coef, every) with every > 0")
             if params.get("conv") and not 1 <= int(params["conv"]) <= 16:
                 raise ValueError("the short convolution takes 1 to 16 taps")
             if params.get("out_bias") or params.get("keep_first"):

@@ -304,7 +304,7 @@ def qkv_norm_write(qkv, bias, step: StepTensors, kv: KvSlot | None, rotary, num_
             k = k * k_weight.float()
     q, k = rotate(q, positions, rotary), rotate(k, positions, rotary)
     if q_temp is not None:
-        steps = torch.div(positions + 1, int(q_temp[1]), rounding_mode="floor").float()
+        steps = torch.div((positions + 1).float(), float(q_temp[1]), rounding_mode="floor")
         q = q * (1.0 + float(q_temp[0]) * torch.log(steps + 1.0))[:, None, None]
     if kv is not None:
         pos = positions.long()

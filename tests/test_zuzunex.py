@@ -202,7 +202,7 @@ def test_config_reads_every_size_and_names_what_is_missing():
     assert (cfg.vocab, cfg.width, cfg.eps, cfg.logit_scale, len(cfg.layers), cfg.loop) == (101, 72, 1e-6, 1.0, 5, None)
     first = cfg.layers[0].mixer
     assert (first.heads, first.kv_heads, first.dim, first.vdim, first.scale) == (1, 1, 24, 10, 0.2)
-    assert (first.softcap, first.temp_coef, first.temp_every, first.biases, first.conv, first.rot_dims) == (None, 1.3, 1, False, None, None)
+    assert (first.softcap, first.temp_coef, first.temp_every, first.biases, first.conv, first.rot_dims) == (None, 1.3, 1.0, False, None, None)
     last = cfg.layers[4].mixer
     assert (last.conv, last.rot_base, last.rot_dims, last.biases, last.weighted_norm) == (5, 1e6, 4, True, True)
     assert (last.rot_scaling.factor, last.rot_scaling.original, last.rot_scaling.fast, last.rot_scaling.slow) == (8.0, 8.0, 2.0, 0.5)
@@ -547,6 +547,8 @@ ALONE = {
     "bare": [_layer("attention", _plain(2, 2, 16, 16, 0.3), None)],
     "convolved": [_layer("attention_2", _conv(4, 2, 8, 8, 0.4, 3, (300.0, 6), (2.0, 8, 2.0, 1.0)), None)],
     "biased": [_layer("attention_2", _conv(2, 1, 12, 5, 0.4), None)],
+    "one_tap": [_layer("attention_2", _conv(3, 1, 8, 8, 0.4, 1, (100.0, 2)), None)],
+    "odd_steps": [_layer("attention", _plain(2, 2, 8, 8, 0.5, 4.0, (0.6, 2.5)), None)],
     "dense": [_layer("attention", _plain(1, 1, 8, 8, 0.3), _dense(44))],
     "routed": [_layer("attention", _plain(1, 1, 8, 8, 0.3), _moe(6, 2, 3, 20, 28))],
     "again": [_layer("attention_2", _conv(2, 2, 8, 8, 0.4, 4, (50.0, 8)), _dense(24))],
