@@ -274,7 +274,7 @@ def test_random_model_folder_loads_by_its_config(tmp_path):
 
 def test_frequencies_slowed_along_a_ramp():
     for base, dims, scaling in ((1000.0, 8, (3.0, 16, 4.0, 1.0)), (10000.0, 64, (4.0, 64, 8.0, 1.0)), (1e6, 4, (8.0, 8, 2.0, 0.5)),
-                                (5e5, 48, (4.0, 1024, 32.0, 1.0)), (100.0, 16, (2.0, 4096, 1.0, 1.0))):
+                                (2e5, 40, (5.0, 2048, 16.0, 2.0)), (100.0, 16, (2.0, 4096, 1.0, 1.0))):
         want, mult = pz.yarn_frequencies(base, dims, dict(zip(("factor", "original", "fast", "slow"), scaling)))
         got = ramped_frequencies(base, dims, *scaling)
         assert torch.allclose(got.double(), want, rtol=1e-6, atol=0)
