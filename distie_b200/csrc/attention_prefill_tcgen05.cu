@@ -119,7 +119,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                                  int table_width, int group_size, int num_kv_heads, int page_shift, int num_pages,
                                  int window, int key_chunk, int keep_first, float scale_log2, float cap, float cap_pre,
                                  const float* __restrict__ sink_logits, int* __restrict__ error) {
-  // cap > 0: a raw score s becomes cap * tanh(s * cap_pre) (cap_pre = scale / cap) and scale_log2 is log2(e) alone.
+  // cap > 0: a raw score s becomes tanh(s * cap_pre) (cap_pre = scale / cap) and scale_log2 is cap * log2(e): the
+  // cap's own factor rides the multiplication by scale_log2 that every score goes through anyway.
   // sink_logits: one float per head whose exponential joins the row's sum at the end (null: none).
   extern __shared__ unsigned char raw[];
   auto& sm = *reinterpret_cast<AttnShared<D>*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
@@ -330,9 +331,15 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       uint32_t sv[kAttnGroupKeys];
       tmem_load_64(s_addr, sv);
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      if (cap > 0.f) {  // one more special-function instruction per score
+      if (cap > 0.f) {  // one more special-function instruction per score, and a multiplication per pair of scores
+        const uint64_t pre2 = pair_of(cap_pre, cap_pre), zero2 = pair_of(0.f, 0.f);
 #pragma unroll
-        for (int i = 0; i < kAttnGroupKeys; ++i) sv[i] = __float_as_uint(cap * tanh_fast(__uint_as_float(sv[i]) * cap_pre));
+        for (int i = 0; i < kAttnGroupKeys; i += 2) {
+          float x0, x1;
+          halves_of(fma_pairs(pair_of(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])), pre2, zero2), x0, x1);
+          sv[i] = __float_as_uint(tanh_fast(x0));
+          sv[i + 1] = __float_as_uint(tanh_fast(x1));
+        }
       }
       if (!unmasked) {
 #pragma unroll
@@ -555,7 +562,7 @@ extern "C" int distie_attention_prefill_tcgen05(const void* q, int q_row_stride,
   if ((status = make_map(&map_k, k_cache, (int)cache_rows, head_dim, head_dim, page_size)) != 0) return status;
   if ((status = make_map(&map_v, v_cache, (int)cache_rows, head_dim, head_dim, page_size)) != 0) return status;
   const float cap = softcap > 0.f ? softcap : 0.f, cap_pre = cap > 0.f ? scale / cap : 0.f;
-  const float scale_log2 = (cap > 0.f ? 1.f : scale) * 1.4426950408889634f;
+  const float scale_log2 = (cap > 0.f ? cap : scale) * 1.4426950408889634f;
   if (head_dim == 64)
     return launch_attention_tc<64>(map_q, map_k, map_v, map_out, out, out_row_stride, q_tiles, num_tiles, positions, token_seq,
                                    seq_seat, block_table, table_width, num_heads, num_kv_heads, page_shift, num_pages,
